@@ -1,0 +1,163 @@
+"""ctypes binding of libpaged_attention_b200.so (include/paged_attention_b200.h).
+
+This is the only place that touches the shared library; the ``lib`` modules and
+the tests go through it.  The library is loaded from this package directory and
+nowhere else, and a missing library is an error (no fallback path exists).
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+KV_F16 = 0
+KV_FP8_E5M2 = 1
+KV_FP8_E4M3 = 2
+
+PA_OK = 0
+PA_ERR_UNSUPPORTED = 1
+PA_ERR_BAD_ARG = 2
+PA_ERR_CUDA = 3
+PA_ERR_TIMEOUT = 4
+
+_LIB_NAME = "libpaged_attention_b200.so"
+_lib = None
+
+EXPORTED_SYMBOLS = (
+    "launch_kernels_loop",
+    "launch_kernels_reduce",
+    "launch_kernels_fp8_loop",
+    "launch_kernels_fp8_reduce",
+    "pa_query_policy",
+    "pa_partition_size",
+    "pa_last_error",
+    "pa_device_status",
+    "pa_version",
+)
+
+
+class PaParams(ctypes.Structure):
+    """struct pa_params of include/paged_attention_b200.h (field order matters)."""
+
+    _fields_ = [
+        ("out", ctypes.c_void_p),
+        ("max_logits", ctypes.c_void_p),
+        ("exp_sums", ctypes.c_void_p),
+        ("tmp_out", ctypes.c_void_p),
+        ("query", ctypes.c_void_p),
+        ("key_cache", ctypes.c_void_p),
+        ("value_cache", ctypes.c_void_p),
+        ("sinks", ctypes.c_void_p),
+        ("block_tables", ctypes.c_void_p),
+        ("context_lens", ctypes.c_void_p),
+        ("num_seqs", ctypes.c_uint32),
+        ("num_heads", ctypes.c_uint32),
+        ("head_size", ctypes.c_uint32),
+        ("num_kv_heads", ctypes.c_uint32),
+        ("max_num_partitions", ctypes.c_uint32),
+        ("max_blocks_per_seq", ctypes.c_uint32),
+        ("block_size", ctypes.c_uint32),
+        ("num_queries_per_tokens", ctypes.c_uint32),
+        ("max_context_len", ctypes.c_uint32),
+        ("reserved0", ctypes.c_uint32),
+        ("num_blocks", ctypes.c_uint64),
+        ("sm_scale", ctypes.c_float),
+        ("fp8_scale", ctypes.c_float),
+        ("kv_dtype", ctypes.c_int32),
+        ("reserved1", ctypes.c_int32),
+    ]
+
+
+class PaPolicyInfo(ctypes.Structure):
+    """struct pa_policy_info of include/paged_attention_b200.h."""
+
+    _fields_ = [
+        ("partition_size", ctypes.c_uint32),
+        ("stages", ctypes.c_uint32),
+        ("head_size_stride", ctypes.c_uint32),
+        ("partition_stride", ctypes.c_uint32),
+        ("max_partitions_per_sg", ctypes.c_uint32),
+        ("tokens_per_stage", ctypes.c_uint32),
+        ("ring_stages", ctypes.c_uint32),
+        ("ring_stages_fp8", ctypes.c_uint32),
+        ("consumer_warps", ctypes.c_uint32),
+        ("threads_per_cta", ctypes.c_uint32),
+    ]
+
+
+def library_path() -> Path:
+    return Path(__file__).resolve().parent / _LIB_NAME
+
+
+def load_library() -> ctypes.CDLL:
+    """Loads the shared library (once) and declares the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not path.exists():
+        raise RuntimeError(
+            f"{path} is missing: build it with `python -m flash_attention_factory_b200.build` "
+            "(there is no CPU or PyTorch fallback)"
+        )
+    lib = ctypes.CDLL(str(path))
+    launcher_args = [ctypes.POINTER(PaParams), ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]
+    for name in ("launch_kernels_loop", "launch_kernels_reduce", "launch_kernels_fp8_loop",
+                 "launch_kernels_fp8_reduce"):
+        fn = getattr(lib, name)
+        fn.argtypes = launcher_args
+        fn.restype = ctypes.c_int
+    lib.pa_query_policy.argtypes = [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
+                                    ctypes.POINTER(PaPolicyInfo)]
+    lib.pa_query_policy.restype = ctypes.c_int
+    lib.pa_partition_size.argtypes = [ctypes.c_uint32]
+    lib.pa_partition_size.restype = ctypes.c_uint32
+    lib.pa_last_error.argtypes = []
+    lib.pa_last_error.restype = ctypes.c_char_p
+    lib.pa_device_status.argtypes = []
+    lib.pa_device_status.restype = ctypes.c_int
+    lib.pa_version.argtypes = []
+    lib.pa_version.restype = ctypes.c_char_p
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load_library().pa_last_error().decode()
+
+
+def check(rc: int) -> None:
+    """Turns a pa_status into the exception the reference would have thrown.
+
+    The reference throws std::runtime_error, which pybind11 surfaces as
+    RuntimeError (paged_attention_loop/launch_kernels_loop.h:114-115,170-172).
+    """
+    if rc != PA_OK:
+        raise RuntimeError(last_error())
+
+
+def query_policy(head_size: int, block_size: int, group: int) -> PaPolicyInfo:
+    info = PaPolicyInfo()
+    check(load_library().pa_query_policy(head_size, block_size, group, ctypes.byref(info)))
+    return info
+
+
+def partition_size(head_size: int) -> int:
+    return int(load_library().pa_partition_size(head_size))
+
+
+def device_status() -> None:
+    """Synchronises the current device and raises if a kernel gave up a bounded wait."""
+    check(load_library().pa_device_status())
+
+
+def launch(entry: str, params: PaParams, stream: int, timed: bool) -> list[float]:
+    """Calls one launcher.  ``timed`` selects the blocking form that returns microseconds."""
+    lib = load_library()
+    fn = getattr(lib, entry)
+    n_times = 2 if entry.endswith("reduce") else 1
+    if timed:
+        buf = (ctypes.c_float * 2)()
+        check(fn(ctypes.byref(params), ctypes.c_void_p(stream), buf))
+        return [float(buf[i]) for i in range(n_times)]
+    check(fn(ctypes.byref(params), ctypes.c_void_p(stream), None))
+    return []

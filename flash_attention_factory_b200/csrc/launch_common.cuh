@@ -1,0 +1,269 @@
+// Host side shared by the four launchers: argument validation, TMA descriptor
+// encoding, the run-time -> compile-time dispatch on (head_size, kv type), the
+// launch geometry and the optional blocking timing.  Mirrors what the
+// reference's dispatch_* / launch_* pairs do on the host
+// (reference paged_attention_loop/launch_kernels_loop.h:16-54,56-173 and
+// paged_attention_reduce/launch_kernels_reduce.h:18-78,80-197).
+#pragma once
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "paged_attention_b200.h"
+#include "paged_attention_kernels.cuh"
+
+namespace pa {
+
+// ------------------------------------------------------------------ errors
+void set_last_error(const char *fmt, ...); // defined in c_api.cu
+int fail(int code, const char *fmt, ...);  // sets the message, returns code
+
+#define PA_CUDA_TRY(expr)                                                               \
+  do {                                                                                  \
+    cudaError_t err__ = (expr);                                                         \
+    if (err__ != cudaSuccess)                                                           \
+      return ::pa::fail(PA_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__)); \
+  } while (0)
+
+// ------------------------------------------------------- TMA descriptor setup
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_tiled(); // defined in c_api.cu; nullptr if the driver lacks it
+
+// Describes one cache tensor [num_blocks*block_size rows, num_kv_heads*head_size elems]
+// with a box of (slab_elems x rows_per_box); rows past num_blocks*block_size read as zero.
+template <int D, int KV>
+int encode_cache_map(CUtensorMap *map, const void *cache, const pa_params *p, uint32_t rows_per_box) {
+  using geo = kv_tile_geometry<D, KV>;
+  EncodeTiledFn encode = get_encode_tiled();
+  if (encode == nullptr) return fail(PA_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(p->num_kv_heads) * D,
+                              static_cast<cuuint64_t>(p->num_blocks) * p->block_size};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p->num_kv_heads) * D * geo::elt_bytes};
+  const cuuint32_t box[2] = {geo::slab_elems, rows_per_box};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUtensorMapDataType dt =
+      (KV == KV_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUtensorMapSwizzle sw =
+      (geo::slab_bytes == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const CUresult r = encode(map, dt, 2, const_cast<void *>(cache), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return PA_OK;
+}
+
+// ----------------------------------------------------------------- validation
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Checks shared by all entry points.  `fp8_entry` selects which kv_dtype values
+// the entry point accepts; `needs_scratch` is true for the split variant.
+inline int validate_params(const pa_params *p, bool fp8_entry, bool needs_scratch) {
+  if (p == nullptr) return fail(PA_ERR_BAD_ARG, "params is null");
+  // the two checks the reference makes, with its messages
+  // (launch_kernels_loop.h:114-115,170-172)
+  const bool head_ok = p->head_size == 128 || p->head_size == 64;
+  const bool block_ok = p->block_size == 16 || p->block_size == 32 || p->block_size == 64 ||
+                        p->block_size == 128;
+  if (!head_ok || !block_ok) return fail(PA_ERR_UNSUPPORTED, "Unsupported head size or block size");
+  if (p->num_queries_per_tokens < 1 || p->num_queries_per_tokens > 8)
+    return fail(PA_ERR_UNSUPPORTED, "Unsupported number of queries per token");
+  if (fp8_entry) {
+    if (p->kv_dtype != PA_KV_FP8_E5M2 && p->kv_dtype != PA_KV_FP8_E4M3)
+      return fail(PA_ERR_BAD_ARG, "FP8 entry point needs kv_dtype e5m2 or e4m3, got %d", p->kv_dtype);
+  } else if (p->kv_dtype != PA_KV_F16) {
+    return fail(PA_ERR_BAD_ARG, "fp16 entry point needs kv_dtype f16, got %d", p->kv_dtype);
+  }
+  if (p->num_seqs == 0) return PA_OK; // nothing to do; the launcher returns early
+  if (!p->out || !p->query || !p->key_cache || !p->value_cache || !p->block_tables || !p->context_lens)
+    return fail(PA_ERR_BAD_ARG, "a required pointer is null");
+  if (p->num_kv_heads == 0 || p->num_heads != p->num_kv_heads * p->num_queries_per_tokens)
+    return fail(PA_ERR_BAD_ARG, "num_heads (%u) != num_kv_heads (%u) * num_queries_per_tokens (%u)",
+                p->num_heads, p->num_kv_heads, p->num_queries_per_tokens);
+  if (p->num_blocks == 0 || p->max_blocks_per_seq == 0)
+    return fail(PA_ERR_BAD_ARG, "num_blocks and max_blocks_per_seq must be positive");
+  if (p->num_blocks * p->block_size >= (1ull << 31))
+    return fail(PA_ERR_BAD_ARG, "cache has too many token rows for a 32-bit TMA coordinate");
+  if (p->num_seqs > 65535u || p->num_kv_heads > 65535u)
+    return fail(PA_ERR_BAD_ARG, "num_seqs and num_kv_heads are limited to 65535");
+  if (!aligned16(p->key_cache) || !aligned16(p->value_cache))
+    return fail(PA_ERR_BAD_ARG, "key_cache / value_cache must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(p->query) & 3u) || (reinterpret_cast<uintptr_t>(p->out) & 1u))
+    return fail(PA_ERR_BAD_ARG, "query / out are misaligned");
+  if (needs_scratch) {
+    if (!p->max_logits || !p->exp_sums || !p->tmp_out)
+      return fail(PA_ERR_BAD_ARG, "the reduce variant needs max_logits, exp_sums and tmp_out");
+    if (p->max_num_partitions == 0 || p->max_num_partitions > 65535u)
+      return fail(PA_ERR_BAD_ARG, "max_num_partitions must be in 1..65535");
+    if (reinterpret_cast<uintptr_t>(p->tmp_out) & 7u)
+      return fail(PA_ERR_BAD_ARG, "tmp_out must be 8-byte aligned");
+  }
+  return PA_OK;
+}
+
+// ------------------------------------------------------------------ geometry
+struct DeviceInfo {
+  int sm_count;
+  int cc_major;
+};
+int get_device_info(DeviceInfo *info); // cached per device; defined in c_api.cu
+
+// Cluster size of the loop variant: enough CTAs to give every SM two, using
+// only what the host knows (num_seqs, num_kv_heads and the context-length hint).
+inline uint32_t choose_cluster_size(const pa_params *p, int sm_count, uint32_t tokens_per_stage) {
+  const uint64_t units = static_cast<uint64_t>(p->num_seqs) * p->num_kv_heads;
+  const uint64_t want = 2ull * static_cast<uint64_t>(sm_count);
+  uint32_t cs = 1;
+  while (cs < 8 && units * cs < want) cs *= 2;
+  if (p->max_context_len != 0) {
+    // no point in more CTAs than stages of the longest context
+    const uint32_t stages = divide_round_up(p->max_context_len, tokens_per_stage);
+    while (cs > 1 && cs > stages) cs /= 2;
+  }
+  return cs;
+}
+
+template <int D, int KV>
+AttnArgs make_attn_args(const pa_params *p) {
+  using policy = paged_attention_policy_v2<D, KV>;
+  AttnArgs a{};
+  a.query = static_cast<const __half *>(p->query);
+  a.out = static_cast<__half *>(p->out);
+  a.max_logits = p->max_logits;
+  a.exp_sums = p->exp_sums;
+  a.tmp_out = static_cast<__half *>(p->tmp_out);
+  a.sinks = static_cast<const __half *>(p->sinks);
+  a.block_tables = p->block_tables;
+  a.context_lens = p->context_lens;
+  a.num_heads = p->num_heads;
+  a.num_kv_heads = p->num_kv_heads;
+  a.group = p->num_queries_per_tokens;
+  a.max_blocks_per_seq = p->max_blocks_per_seq;
+  a.max_num_partitions = p->max_num_partitions;
+  a.block_shift = log2_pow2(p->block_size);
+  a.rows_per_box = p->block_size < policy::tokens_per_stage ? p->block_size : policy::tokens_per_stage;
+  a.boxes_per_stage = policy::tokens_per_stage / a.rows_per_box;
+  const float kv_scale = (KV == KV_F16) ? 1.f : p->fp8_scale;
+  // the FP8 scale is applied once, hoisted out of the dot products
+  // (reference paged_attention_kernel_fp8_loop.hpp:333,545)
+  a.scale_log2 = p->sm_scale * kv_scale * kLog2e;
+  a.out_scale = kv_scale;
+  return a;
+}
+
+// Enqueues the attention kernel of one (D, KV, MODE) instantiation.
+template <int D, int KV, int MODE>
+int enqueue_attention(const pa_params *p, cudaStream_t stream) {
+  using L = SmemLayout<D, KV>;
+  using policy = typename L::policy;
+  DeviceInfo dev{};
+  if (int rc = get_device_info(&dev)) return rc;
+  if (dev.cc_major < 10) return fail(PA_ERR_CUDA, "this library needs an sm_100a device");
+
+  AttnArgs args = make_attn_args<D, KV>(p);
+  CUtensorMap map_k, map_v;
+  if (int rc = encode_cache_map<D, KV>(&map_k, p->key_cache, p, args.rows_per_box)) return rc;
+  if (int rc = encode_cache_map<D, KV>(&map_v, p->value_cache, p, args.rows_per_box)) return rc;
+
+  auto kernel = paged_attention_kernel<D, KV, MODE>;
+  static thread_local int configured_device = -1;
+  int device = 0;
+  PA_CUDA_TRY(cudaGetDevice(&device));
+  if (configured_device != device) {
+    PA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM));
+    configured_device = device;
+  }
+
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  cfg.blockDim = dim3(policy::threads_per_cta, 1, 1);
+  cfg.dynamicSmemBytes = L::DYN_SMEM;
+  cfg.stream = stream;
+  if (MODE == MODE_SPLIT) {
+    // kv head fastest: CTAs that run together read neighbouring rows of the same KV blocks
+    cfg.gridDim = dim3(p->num_kv_heads, p->max_num_partitions, p->num_seqs);
+    cfg.numAttrs = 0;
+  } else {
+    const uint32_t cs = choose_cluster_size(p, dev.sm_count, policy::tokens_per_stage);
+    cfg.gridDim = dim3(cs, p->num_kv_heads, p->num_seqs);
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_k, map_v, args));
+  return PA_OK;
+}
+
+template <int D>
+int enqueue_merge(const pa_params *p, cudaStream_t stream) {
+  const uint32_t psize = (D == 64) ? 256u : 512u;
+  merge_partitions_kernel<D><<<dim3(p->num_heads, p->num_seqs), 128, 0, stream>>>(
+      static_cast<__half *>(p->out), static_cast<const __half *>(p->tmp_out), p->max_logits,
+      p->exp_sums, p->context_lens, p->num_heads, p->max_num_partitions, psize);
+  PA_CUDA_TRY(cudaGetLastError());
+  return PA_OK;
+}
+
+// Runs `first` and (if non-null) `second` on `stream`.  With us_out the call
+// records events around each step, blocks, and reports device microseconds.
+template <typename F1, typename F2>
+int run_timed(cudaStream_t stream, float *us_out, F1 first, F2 second, bool has_second) {
+  if (us_out == nullptr) {
+    if (int rc = first()) return rc;
+    if (has_second) return second();
+    return PA_OK;
+  }
+  cudaEvent_t ev[3];
+  for (auto &e : ev) PA_CUDA_TRY(cudaEventCreate(&e));
+  int rc = PA_OK;
+  cudaError_t err = cudaEventRecord(ev[0], stream);
+  if (err == cudaSuccess) rc = first();
+  if (rc == PA_OK && err == cudaSuccess) err = cudaEventRecord(ev[1], stream);
+  if (rc == PA_OK && err == cudaSuccess && has_second) {
+    rc = second();
+    if (rc == PA_OK) err = cudaEventRecord(ev[2], stream);
+  }
+  if (rc == PA_OK && err == cudaSuccess) err = cudaEventSynchronize(has_second ? ev[2] : ev[1]);
+  if (rc == PA_OK && err == cudaSuccess) {
+    float ms = 0.f;
+    err = cudaEventElapsedTime(&ms, ev[0], ev[1]);
+    us_out[0] = ms * 1000.f;
+    if (has_second && err == cudaSuccess) {
+      err = cudaEventElapsedTime(&ms, ev[1], ev[2]);
+      us_out[1] = ms * 1000.f;
+    }
+  }
+  for (auto &e : ev) cudaEventDestroy(e);
+  if (rc != PA_OK) return rc;
+  if (err != cudaSuccess) return fail(PA_ERR_CUDA, "CUDA error while timing: %s", cudaGetErrorString(err));
+  return PA_OK;
+}
+
+// head-size dispatch for one KV type and mode
+template <int KV, int MODE>
+int dispatch_head_size(const pa_params *p, cudaStream_t stream) {
+  if (p->head_size == 128) return enqueue_attention<128, KV, MODE>(p, stream);
+  return enqueue_attention<64, KV, MODE>(p, stream);
+}
+
+inline int dispatch_merge(const pa_params *p, cudaStream_t stream) {
+  if (p->head_size == 128) return enqueue_merge<128>(p, stream);
+  return enqueue_merge<64>(p, stream);
+}
+
+// reads and clears this translation unit's copy of the device status word
+inline int read_and_clear_device_status(int *value) {
+  int v = 0, zero = 0;
+  PA_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_pa_device_status, sizeof(int)));
+  if (v != 0) PA_CUDA_TRY(cudaMemcpyToSymbol(g_pa_device_status, &zero, sizeof(int)));
+  *value = v;
+  return PA_OK;
+}
+
+} // namespace pa

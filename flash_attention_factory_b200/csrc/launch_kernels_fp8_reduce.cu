@@ -1,0 +1,22 @@
+// launch_kernels_fp8_reduce: FP8 (e5m2 / e4m3) KV cache, split-context decode
+// attention.  Host counterpart of the reference's dispatch_paged_attention_fp8 /
+// launch_paged_attn_fp8_v2
+// (paged_attention_fp8_reduce/launch_kernels_fp8_reduce.h:16-76,78-196).
+#include "launch_common.cuh"
+
+namespace pa {
+int read_status_fp8_reduce(int *v) { return read_and_clear_device_status(v); }
+} // namespace pa
+
+extern "C" PA_API int launch_kernels_fp8_reduce(const pa_params *p, void *stream, float *us_out) {
+  using namespace pa;
+  if (int rc = validate_params(p, /*fp8_entry=*/true, /*needs_scratch=*/true)) return rc;
+  if (us_out) us_out[0] = us_out[1] = 0.f;
+  if (p->num_seqs == 0) return PA_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto attn = [&] {
+    return p->kv_dtype == PA_KV_FP8_E5M2 ? dispatch_head_size<KV_E5M2, MODE_SPLIT>(p, s)
+                                         : dispatch_head_size<KV_E4M3, MODE_SPLIT>(p, s);
+  };
+  return run_timed(s, us_out, attn, [&] { return dispatch_merge(p, s); }, true);
+}

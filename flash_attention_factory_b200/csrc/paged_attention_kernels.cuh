@@ -1,0 +1,601 @@
+// Device kernels of the B200 paged-attention decode library (sm_100a).
+//
+// One templated attention kernel serves the four entry points:
+//   MODE_LOOP   one (sequence, KV head) per thread-block cluster, the context
+//               split over the cluster's CTAs and merged through distributed
+//               shared memory; writes `out`
+//               (reference paged_attention_loop_kernel, paged_attention_kernel_loop.hpp:42-637)
+//   MODE_SPLIT  one (sequence, KV head, partition) per CTA; writes max_logits,
+//               exp_sums and the fp16 partial output
+//               (reference paged_attention_kernel, paged_attention_kernel_v2.hpp:42-588)
+// with the KV cache stored as fp16, e5m2 or e4m3 (FP8 dequantised in
+// registers, reference paged_attention_kernel_fp8_loop.hpp:270-278,328-333,540-545).
+// merge_partitions_kernel is the second kernel of the split variant
+// (reference paged_attention_reduce, paged_attention_kernel_v2.hpp:594-970).
+//
+// Structure of the attention kernel: warp 0 walks the block table and issues
+// tiled TMA copies (one box per KV block and 128-byte slab) into a ring of
+// shared-memory stages guarded by full/empty mbarriers; warps 1..4 each own 16
+// tokens of every stage.  The GQA query group sits on the N=8 extent of
+// mma.m16n8k16 and the tokens on M, so a KV byte is read from HBM once for the
+// whole group:
+//   S^T[tok, g] = K[tok, d] . Q^T[d, g]          (A = K via ldmatrix)
+//   O^T[d, g]  += V^T[d, tok] . P^T[tok, g]      (A = V via ldmatrix.trans)
+// Softmax is online per warp in the log2 domain with warp-shuffle column
+// maxima; the four warps' (max, sum, acc) are merged through shared memory at
+// the end.  Every wait on an mbarrier is bounded (pa::mbar_wait_bounded).
+#pragma once
+
+#include <cooperative_groups.h>
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "paged_attention_policy_v2.hpp"
+#include "paged_attention_utils.hpp"
+
+namespace pa {
+
+enum Mode : int { MODE_LOOP = 0, MODE_SPLIT = 1 };
+
+// Set when a bounded wait gave up; read and cleared by pa_device_status().
+// One copy per translation unit (the launchers are compiled separately).
+static __device__ int g_pa_device_status = 0;
+
+struct AttnArgs {
+  const __half *query;
+  __half *out;
+  float *max_logits;
+  float *exp_sums;
+  __half *tmp_out;
+  const __half *sinks; // nullable
+  const uint32_t *block_tables;
+  const uint32_t *context_lens;
+  uint32_t num_heads;
+  uint32_t num_kv_heads;
+  uint32_t group;
+  uint32_t max_blocks_per_seq;
+  uint32_t max_num_partitions;
+  uint32_t block_shift;     // log2(block_size)
+  uint32_t rows_per_box;    // min(block_size, tokens_per_stage)
+  uint32_t boxes_per_stage; // tokens_per_stage / rows_per_box
+  float scale_log2;         // sm_scale * fp8_scale * log2(e)
+  float out_scale;          // fp8_scale (1 for fp16)
+};
+
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D, int KV>
+struct SmemLayout {
+  using policy = paged_attention_policy_v2<D, KV>;
+  using geo = typename policy::geometry;
+  static constexpr uint32_t NW = policy::consumer_warps;
+  static constexpr uint32_t TS = policy::tokens_per_stage;
+  static constexpr uint32_t NSTAGES = policy::ring_stages;
+  static constexpr uint32_t SLAB_TILE = TS * geo::slab_bytes;         // one slab of one stage
+  static constexpr uint32_t KV_TILE = geo::num_slabs * SLAB_TILE;     // K (or V) of one stage
+  static constexpr uint32_t STAGE_BYTES = 2 * KV_TILE;
+  static constexpr uint32_t RING_BYTES = NSTAGES * STAGE_BYTES;
+  // merge scratch, aliased on the ring once every stage has been consumed
+  static constexpr uint32_t WARP_AREA_FLOATS = 8 * D + 16; // O[8][D], m[8], l[8]
+  static constexpr uint32_t MERGE_BYTES = (NW + 1) * WARP_AREA_FLOATS * 4;
+  static_assert(MERGE_BYTES <= RING_BYTES, "merge scratch must fit in the ring");
+  static constexpr uint32_t BAR_OFFSET = RING_BYTES;
+  static constexpr uint32_t TOTAL_BYTES = RING_BYTES + 2 * NSTAGES * 8 + 16;
+  static constexpr uint32_t DYN_SMEM = TOTAL_BYTES + 1024; // slack for 1024-byte alignment
+};
+
+// d index of accumulator tile `tile`, row half `h` (0: rows gid, 1: rows gid+8)
+template <int KV>
+__device__ __forceinline__ uint32_t acc_dim_index(uint32_t tile, uint32_t h, uint32_t gid) {
+  if constexpr (KV == KV_F16) {
+    return tile * 16u + h * 8u + gid;
+  } else {
+    // FP8: tiles come in (even, odd) byte pairs of a 32-dim group
+    return (tile >> 1) * 32u + h * 16u + 2u * gid + (tile & 1u);
+  }
+}
+
+template <int D, int KV, int MODE>
+__global__ void __launch_bounds__(paged_attention_policy_v2<D, KV>::threads_per_cta, 2)
+paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v, const AttnArgs args) {
+  using L = SmemLayout<D, KV>;
+  using policy = typename L::policy;
+  using geo = typename L::geo;
+  constexpr uint32_t NW = L::NW;
+  constexpr uint32_t TS = L::TS;
+  constexpr uint32_t NSTAGES = L::NSTAGES;
+  constexpr uint32_t KSTEPS = D / 16; // MMA k-steps of QK^T == accumulator tiles of PV
+
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment of the ring makes the TMA swizzle a function of (row, chunk).
+  // The offset is identical in every CTA, so cluster-mapped addresses line up.
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t *smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + L::BAR_OFFSET);
+  uint64_t *empty_bar = full_bar + NSTAGES;
+  volatile uint32_t *abort_flag =
+      reinterpret_cast<volatile uint32_t *>(smem + L::BAR_OFFSET + 2 * NSTAGES * 8);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+
+  // ---- which tokens does this CTA own? (integer bookkeeping, bit-exact)
+  uint32_t seq, kv_head, partition = 0, cta_rank = 0, num_ranks = 1;
+  if constexpr (MODE == MODE_SPLIT) {
+    kv_head = blockIdx.x;
+    partition = blockIdx.y;
+    seq = blockIdx.z;
+  } else {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cta_rank = cluster.block_rank();
+    num_ranks = cluster.num_blocks();
+    kv_head = blockIdx.y;
+    seq = blockIdx.z;
+  }
+  const uint32_t ctx = args.context_lens[seq];
+  uint32_t tok_begin, tok_end;
+  if constexpr (MODE == MODE_SPLIT) {
+    tok_begin = partition * policy::partition_size;
+    if (tok_begin >= ctx) return; // partition past the context: scratch rows stay untouched
+    tok_end = min(ctx, tok_begin + policy::partition_size);
+  } else {
+    const uint32_t total_stages = divide_round_up(ctx, TS);
+    const uint32_t stages_per_rank = divide_round_up(total_stages, num_ranks);
+    tok_begin = min(ctx, cta_rank * stages_per_rank * TS);
+    tok_end = min(ctx, (cta_rank + 1) * stages_per_rank * TS);
+  }
+  const uint32_t my_tokens = tok_end - tok_begin;
+  const uint32_t my_stages = divide_round_up(my_tokens, TS);
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < NSTAGES; ++s) {
+      mbar_init(&full_bar[s], 1);   // one arrive.expect_tx by the producer
+      mbar_init(&empty_bar[s], NW); // one arrive per consumer warp
+    }
+    *abort_flag = 0u;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == 0) {
+    // =========================== producer warp ===========================
+    if (lane == 0) {
+      tma_prefetch_descriptor(&tmap_k);
+      tma_prefetch_descriptor(&tmap_v);
+    }
+    const uint32_t rows = args.rows_per_box;
+    const uint32_t bps = args.boxes_per_stage;
+    const uint32_t total_boxes = divide_round_up(my_tokens, rows);
+    const uint32_t *table = args.block_tables + static_cast<size_t>(seq) * args.max_blocks_per_seq;
+    const uint32_t box_bytes = rows * geo::row_bytes; // K (or V) bytes of one box
+    const uint32_t ring_base = smem_u32(smem);
+    const int32_t x0 = static_cast<int32_t>(kv_head * D);
+    bool alive = true;
+
+    auto fetch_block_id = [&](uint32_t box) -> uint32_t {
+      if (box >= total_boxes) return 0u;
+      const uint32_t tok = tok_begin + box * rows;
+      return __ldg(table + (tok >> args.block_shift));
+    };
+    uint32_t block_id_next = fetch_block_id(lane);
+    for (uint32_t batch0 = 0; batch0 < total_boxes && alive; batch0 += 32) {
+      const uint32_t box = batch0 + lane;
+      const uint32_t block_id = block_id_next;
+      block_id_next = fetch_block_id(box + 32); // prefetch the next batch of table entries
+      const bool valid = box < total_boxes;
+      const uint32_t tok = tok_begin + box * rows;
+      const int32_t y = static_cast<int32_t>((block_id << args.block_shift) +
+                                             (tok & ((1u << args.block_shift) - 1u)));
+      const uint32_t first_stage = batch0 / bps;
+      const uint32_t last_box = min(batch0 + 31u, total_boxes - 1u);
+      const uint32_t last_stage = last_box / bps;
+      for (uint32_t st = first_stage; st <= last_stage; ++st) {
+        const uint32_t slot = st % NSTAGES;
+        const uint32_t phase = (st / NSTAGES) & 1u;
+        if (lane == 0) {
+          alive = mbar_wait_bounded(&empty_bar[slot], phase ^ 1u, abort_flag);
+          if (alive) {
+            const uint32_t boxes_here = min(bps, total_boxes - st * bps);
+            mbar_arrive_expect_tx(&full_bar[slot], boxes_here * box_bytes * 2u);
+          }
+        }
+        alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+        if (!alive) break;
+        if (valid && box / bps == st) {
+          const uint32_t row0 = (box % bps) * rows;
+          const uint32_t stage_base = ring_base + slot * L::STAGE_BYTES;
+#pragma unroll
+          for (uint32_t sl = 0; sl < geo::num_slabs; ++sl) {
+            const uint32_t dst = stage_base + sl * L::SLAB_TILE + row0 * geo::slab_bytes;
+            const int32_t x = x0 + static_cast<int32_t>(sl * geo::slab_elems);
+            tma_load_2d(dst, &tmap_k, &full_bar[slot], x, y);
+            tma_load_2d(dst + L::KV_TILE, &tmap_v, &full_bar[slot], x, y);
+          }
+        }
+      }
+    }
+  } else {
+    // =========================== consumer warps ==========================
+    const uint32_t cw = warp - 1; // 0..NW-1
+    const uint32_t gid = lane >> 2;
+    const uint32_t t4 = lane & 3u;
+    const uint32_t G = args.group;
+
+    // Q fragments (B operand, n = gid is the query head inside the group)
+    uint32_t qf[KSTEPS][2];
+    {
+      const __half *qrow = args.query +
+                           (static_cast<size_t>(seq) * args.num_heads + kv_head * G + gid) * D;
+#pragma unroll
+      for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+        if (gid < G) {
+          if constexpr (KV == KV_F16) {
+            qf[ks][0] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 2 * t4);
+            qf[ks][1] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 8 + 2 * t4);
+          } else {
+            // FP8 K fragments take 4 consecutive bytes per lane, so the k slots of
+            // an MMA step map to dims 16*ks + 4*t4 + {0,1} and + {2,3}
+            qf[ks][0] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 4 * t4);
+            qf[ks][1] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 4 * t4 + 2);
+          }
+        } else {
+          qf[ks][0] = 0u;
+          qf[ks][1] = 0u;
+        }
+      }
+    }
+
+    // running softmax state of columns g = 2*t4 and 2*t4+1, in the log2 domain
+    float m_run[2] = {neg_infinity(), neg_infinity()};
+    float l_run[2] = {0.f, 0.f}; // per-lane partial sums; reduced over gid at the end
+    float acc[KSTEPS][4];
+#pragma unroll
+    for (uint32_t i = 0; i < KSTEPS; ++i) {
+      acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    }
+    // The sink is one extra logit with a zero value vector, attached to the first
+    // tokens of the context only (reference paged_attention_kernel_loop.hpp:387-401).
+    if (args.sinks != nullptr && cw == 0 && tok_begin == 0) {
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) {
+        const uint32_t g = 2 * t4 + j;
+        if (g < G) {
+          m_run[j] = __half2float(args.sinks[kv_head * G + g]) * kLog2e;
+          l_run[j] = (gid == 0) ? 1.f : 0.f;
+        }
+      }
+    }
+
+    const uint32_t ring_base = smem_u32(smem);
+    // lane-dependent parts of the ldmatrix addresses
+    const uint32_t lm_row_k = cw * 16 + (lane & 7u) + ((lane >> 3) & 1u) * 8u; // K, and FP8 V
+    const uint32_t lm_chunk_k = lane >> 4;
+    const uint32_t lm_row_v = cw * 16 + (lane & 7u) + (lane >> 4) * 8u; // fp16 V (transposed)
+    const uint32_t lm_chunk_v = (lane >> 3) & 1u;
+
+    bool alive = true;
+    for (uint32_t st = 0; st < my_stages && alive; ++st) {
+      const uint32_t slot = st % NSTAGES;
+      const uint32_t phase = (st / NSTAGES) & 1u;
+      alive = mbar_wait_bounded(&full_bar[slot], phase, abort_flag);
+      if (!alive) break;
+      const uint32_t stage_tok0 = st * TS + cw * 16; // first token of this warp's slice
+      if (stage_tok0 < my_tokens) {
+        const uint32_t n_valid = min(16u, my_tokens - stage_tok0);
+        const uint32_t k_base = ring_base + slot * L::STAGE_BYTES;
+        const uint32_t v_base = k_base + L::KV_TILE;
+
+        // ---- S^T = K . Q^T  (two accumulation chains to shorten the dependency)
+        float s_a[4] = {0.f, 0.f, 0.f, 0.f};
+        float s_b[4] = {0.f, 0.f, 0.f, 0.f};
+        if constexpr (KV == KV_F16) {
+#pragma unroll
+          for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+            constexpr uint32_t steps_per_slab = geo::chunks_per_slab / 2;
+            const uint32_t slab = ks / steps_per_slab;
+            const uint32_t chunk0 = 2 * (ks % steps_per_slab);
+            uint32_t a[4];
+            ldmatrix_x4(a, k_base + slab * L::SLAB_TILE +
+                               swizzled_offset<geo::slab_bytes>(lm_row_k, chunk0 + lm_chunk_k));
+            if (ks & 1u) mma_m16n8k16(s_b, a, qf[ks][0], qf[ks][1]);
+            else mma_m16n8k16(s_a, a, qf[ks][0], qf[ks][1]);
+          }
+        } else {
+#pragma unroll
+          for (uint32_t q = 0; q < KSTEPS / 2; ++q) {
+            uint32_t r[4];
+            ldmatrix_x4(r, k_base + swizzled_offset<geo::slab_bytes>(lm_row_k, 2 * q + lm_chunk_k));
+            uint32_t a[4];
+            a[0] = fp8_pair_to_half2<KV, 0, 1>(r[0]);
+            a[1] = fp8_pair_to_half2<KV, 0, 1>(r[1]);
+            a[2] = fp8_pair_to_half2<KV, 2, 3>(r[0]);
+            a[3] = fp8_pair_to_half2<KV, 2, 3>(r[1]);
+            mma_m16n8k16(s_a, a, qf[2 * q][0], qf[2 * q][1]);
+            a[0] = fp8_pair_to_half2<KV, 0, 1>(r[2]);
+            a[1] = fp8_pair_to_half2<KV, 0, 1>(r[3]);
+            a[2] = fp8_pair_to_half2<KV, 2, 3>(r[2]);
+            a[3] = fp8_pair_to_half2<KV, 2, 3>(r[3]);
+            mma_m16n8k16(s_b, a, qf[2 * q + 1][0], qf[2 * q + 1][1]);
+          }
+        }
+        // lane holds S[tok gid][g 2t4, 2t4+1] in [0],[1] and S[tok gid+8][..] in [2],[3]
+        float s[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) s[j] = (s_a[j] + s_b[j]) * args.scale_log2;
+        const bool partial = n_valid < 16u;
+        if (partial) {
+          // tokens past the context never count, whatever the cache holds there
+          // (reference paged_attention_kernel_loop.hpp:323-327)
+          if (gid >= n_valid) s[0] = s[1] = neg_infinity();
+          if (gid + 8 >= n_valid) s[2] = s[3] = neg_infinity();
+        }
+        // ---- online softmax (reference paged_attention_kernel_loop.hpp:382-419)
+        const float tile_max0 = quad_column_max(fmaxf(s[0], s[2]));
+        const float tile_max1 = quad_column_max(fmaxf(s[1], s[3]));
+        const float m_new0 = fmaxf(m_run[0], tile_max0);
+        const float m_new1 = fmaxf(m_run[1], tile_max1);
+        const float r0 = fast_exp2(m_run[0] - m_new0);
+        const float r1 = fast_exp2(m_run[1] - m_new1);
+        m_run[0] = m_new0;
+        m_run[1] = m_new1;
+        const float p0 = fast_exp2(s[0] - m_new0);
+        const float p1 = fast_exp2(s[1] - m_new1);
+        const float p2 = fast_exp2(s[2] - m_new0);
+        const float p3 = fast_exp2(s[3] - m_new1);
+        l_run[0] = l_run[0] * r0 + (p0 + p2); // fp32 sum of the unrounded weights
+        l_run[1] = l_run[1] * r1 + (p1 + p3);
+#pragma unroll
+        for (uint32_t i = 0; i < KSTEPS; ++i) {
+          acc[i][0] *= r0;
+          acc[i][1] *= r1;
+          acc[i][2] *= r0;
+          acc[i][3] *= r1;
+        }
+        // P rounded to fp16 for the MMA, transposed into the B-operand layout
+        const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1)); // tokens 0..7
+        const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3)); // tokens 8..15
+
+        // masks that clear V of tokens past the context, so that 0 * garbage stays 0
+        uint32_t mask_lo = 0xffffffffu, mask_hi = 0xffffffffu;
+        if (partial) {
+          mask_lo = ((2 * t4 < n_valid) ? 0x0000ffffu : 0u) | ((2 * t4 + 1 < n_valid) ? 0xffff0000u : 0u);
+          mask_hi = ((2 * t4 + 8 < n_valid) ? 0x0000ffffu : 0u) | ((2 * t4 + 9 < n_valid) ? 0xffff0000u : 0u);
+        }
+        // ---- O^T += V^T . P^T
+        if constexpr (KV == KV_F16) {
+#pragma unroll
+          for (uint32_t i = 0; i < KSTEPS; ++i) {
+            constexpr uint32_t tiles_per_slab = geo::chunks_per_slab / 2;
+            const uint32_t slab = i / tiles_per_slab;
+            const uint32_t chunk0 = 2 * (i % tiles_per_slab);
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, v_base + slab * L::SLAB_TILE +
+                                     swizzled_offset<geo::slab_bytes>(lm_row_v, chunk0 + lm_chunk_v));
+            if (partial) {
+              a[0] &= mask_lo;
+              a[1] &= mask_lo;
+              a[2] &= mask_hi;
+              a[3] &= mask_hi;
+            }
+            mma_m16n8k16(acc[i], a, pb0, pb1);
+          }
+        } else {
+#pragma unroll
+          for (uint32_t q = 0; q < KSTEPS / 2; ++q) {
+            // 16 tokens x 32 dims of bytes, read as transposed 16-bit units:
+            // r[0]: tokens 0-7 / dims 0-15, r[1]: tokens 8-15 / dims 0-15,
+            // r[2]: tokens 0-7 / dims 16-31, r[3]: tokens 8-15 / dims 16-31.
+            // Each register = {V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1]}.
+            uint32_t r[4];
+            ldmatrix_x4_trans(r, v_base + swizzled_offset<geo::slab_bytes>(lm_row_k, 2 * q + lm_chunk_k));
+            uint32_t a[4];
+            a[0] = fp8_pair_to_half2<KV, 0, 2>(r[0]);
+            a[1] = fp8_pair_to_half2<KV, 0, 2>(r[2]);
+            a[2] = fp8_pair_to_half2<KV, 0, 2>(r[1]);
+            a[3] = fp8_pair_to_half2<KV, 0, 2>(r[3]);
+            if (partial) {
+              a[0] &= mask_lo;
+              a[1] &= mask_lo;
+              a[2] &= mask_hi;
+              a[3] &= mask_hi;
+            }
+            mma_m16n8k16(acc[2 * q], a, pb0, pb1);
+            a[0] = fp8_pair_to_half2<KV, 1, 3>(r[0]);
+            a[1] = fp8_pair_to_half2<KV, 1, 3>(r[2]);
+            a[2] = fp8_pair_to_half2<KV, 1, 3>(r[1]);
+            a[3] = fp8_pair_to_half2<KV, 1, 3>(r[3]);
+            if (partial) {
+              a[0] &= mask_lo;
+              a[1] &= mask_lo;
+              a[2] &= mask_hi;
+              a[3] &= mask_hi;
+            }
+            mma_m16n8k16(acc[2 * q + 1], a, pb0, pb1);
+          }
+        }
+      }
+      // this warp is done with the stage: let the producer refill it
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[slot]);
+    }
+
+    // ---- merge the consumer warps of this CTA through shared memory
+    // every stage has been consumed (or the CTA gave up), so the ring is free
+    named_barrier_sync(1, NW * 32);
+    float *warp_area = reinterpret_cast<float *>(smem) + cw * L::WARP_AREA_FLOATS;
+    l_run[0] = quad_column_sum(l_run[0]);
+    l_run[1] = quad_column_sum(l_run[1]);
+    if (gid == 0) {
+      warp_area[8 * D + 2 * t4] = m_run[0];
+      warp_area[8 * D + 2 * t4 + 1] = m_run[1];
+      warp_area[8 * D + 8 + 2 * t4] = l_run[0];
+      warp_area[8 * D + 8 + 2 * t4 + 1] = l_run[1];
+    }
+#pragma unroll
+    for (uint32_t i = 0; i < KSTEPS; ++i) {
+#pragma unroll
+      for (uint32_t h = 0; h < 2; ++h) {
+        const uint32_t d = acc_dim_index<KV>(i, h, gid);
+        warp_area[(2 * t4) * D + d] = acc[i][2 * h];
+        warp_area[(2 * t4 + 1) * D + d] = acc[i][2 * h + 1];
+      }
+    }
+    named_barrier_sync(1, NW * 32);
+
+    const float *areas = reinterpret_cast<const float *>(smem);
+    float *cta_area = reinterpret_cast<float *>(smem) + NW * L::WARP_AREA_FLOATS;
+    const uint32_t ctid = threadIdx.x - 32; // 0 .. NW*32-1
+    const bool ok = (*abort_flag == 0u);
+    for (uint32_t idx = ctid; idx < 8 * D; idx += NW * 32) {
+      const uint32_t g = idx / D;
+      const uint32_t d = idx % D;
+      float m_all = neg_infinity();
+#pragma unroll
+      for (uint32_t w = 0; w < NW; ++w) m_all = fmaxf(m_all, areas[w * L::WARP_AREA_FLOATS + 8 * D + g]);
+      float l_all = 0.f, o_all = 0.f;
+#pragma unroll
+      for (uint32_t w = 0; w < NW; ++w) {
+        const float mw = areas[w * L::WARP_AREA_FLOATS + 8 * D + g];
+        const float f = (mw == neg_infinity()) ? 0.f : fast_exp2(mw - m_all);
+        l_all += f * areas[w * L::WARP_AREA_FLOATS + 8 * D + 8 + g];
+        o_all += f * areas[w * L::WARP_AREA_FLOATS + g * D + d];
+      }
+      if constexpr (MODE == MODE_SPLIT) {
+        if (g < G && ok) {
+          const size_t head = static_cast<size_t>(seq) * args.num_heads + kv_head * G + g;
+          const size_t pidx = head * args.max_num_partitions + partition;
+          // normalised inside the partition (reference paged_attention_kernel_v2.hpp:386)
+          const float inv = (l_all > 0.f) ? (1.f / l_all) : 0.f;
+          args.tmp_out[pidx * D + d] = __float2half_rn(o_all * args.out_scale * inv);
+          if (d == 0) {
+            args.max_logits[pidx] = m_all * kLn2;
+            args.exp_sums[pidx] = l_all;
+          }
+        }
+      } else {
+        // unnormalised CTA result for the cluster merge
+        cta_area[g * D + d] = o_all;
+        if (d == 0) {
+          cta_area[8 * D + g] = m_all;
+          cta_area[8 * D + 8 + g] = l_all;
+        }
+      }
+    }
+  }
+
+  if constexpr (MODE == MODE_LOOP) {
+    // ---- merge the CTAs of the cluster through distributed shared memory;
+    // every thread of every CTA reaches both cluster barriers, also after an abort
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (warp != 0) {
+      const uint32_t G = args.group;
+      const bool ok = (*abort_flag == 0u);
+      float *cta_area = reinterpret_cast<float *>(smem) + NW * L::WARP_AREA_FLOATS;
+      const uint32_t ctid = threadIdx.x - 32;
+      const uint32_t dims_per_rank = D / num_ranks; // cluster sizes are powers of two <= 8
+      for (uint32_t idx = ctid; idx < 8 * dims_per_rank; idx += NW * 32) {
+        const uint32_t g = idx / dims_per_rank;
+        const uint32_t d = cta_rank * dims_per_rank + idx % dims_per_rank;
+        float m_all = neg_infinity();
+        for (uint32_t r = 0; r < num_ranks; ++r) {
+          const float *peer = cluster.map_shared_rank(cta_area, r);
+          m_all = fmaxf(m_all, peer[8 * D + g]);
+        }
+        float l_all = 0.f, o_all = 0.f;
+        for (uint32_t r = 0; r < num_ranks; ++r) {
+          const float *peer = cluster.map_shared_rank(cta_area, r);
+          const float mr = peer[8 * D + g];
+          const float f = (mr == neg_infinity()) ? 0.f : fast_exp2(mr - m_all);
+          l_all += f * peer[8 * D + 8 + g];
+          o_all += f * peer[g * D + d];
+        }
+        if (g < G && ok) {
+          // acc * (1 / l) as the reference does (paged_attention_utils.hpp:834-835);
+          // an empty context (l = 0) gives zeros
+          const float inv = (l_all > 0.f) ? (1.f / l_all) : 0.f;
+          const size_t head = static_cast<size_t>(seq) * args.num_heads + kv_head * G + g;
+          args.out[head * D + d] = __float2half_rn(o_all * args.out_scale * inv);
+        }
+      }
+    }
+    cluster.sync(); // peers may still be reading this CTA's shared memory
+  }
+  if (threadIdx.x == 32 && *abort_flag != 0u) atomicExch(&g_pa_device_status, 4);
+}
+
+// Second kernel of the split-context variant: one CTA per (sequence, head).
+//   M = max_p m_p ; w_p = l_p * exp(m_p - M) ; W = sum w_p
+//   out[d] = sum_p (w_p / W) * tmp_out[p, d]
+// over the partitions p < ceil(ctx / partition_size) only
+// (reference paged_attention_kernel_v2.hpp:679,736-764,813-863,924-932).
+template <int D>
+__global__ void __launch_bounds__(128)
+merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp_out,
+                        const float *__restrict__ max_logits, const float *__restrict__ exp_sums,
+                        const uint32_t *__restrict__ context_lens, uint32_t num_heads,
+                        uint32_t max_num_partitions, uint32_t partition_size) {
+  constexpr uint32_t LANES_PER_ROW = D / 4; // each lane owns 4 dims (8 bytes)
+  constexpr uint32_t ROWS = 128 / LANES_PER_ROW; // partitions handled in parallel
+  const uint32_t head = blockIdx.x;
+  const uint32_t seq = blockIdx.y;
+  const uint32_t tid = threadIdx.x;
+  const uint32_t ctx = context_lens[seq];
+  const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
+  const size_t base = (static_cast<size_t>(seq) * num_heads + head) * max_num_partitions;
+  __half *orow = out + (static_cast<size_t>(seq) * num_heads + head) * D;
+
+  __shared__ float red[4];
+  __shared__ float part[ROWS][D];
+
+  // global max over partitions
+  float m = neg_infinity();
+  for (uint32_t p = tid; p < np; p += 128) m = fmaxf(m, max_logits[base + p]);
+#pragma unroll
+  for (uint32_t o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((tid & 31u) == 0) red[tid >> 5] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  __syncthreads();
+  // total rescaled weight
+  float wsum = 0.f;
+  for (uint32_t p = tid; p < np; p += 128) wsum += exp_sums[base + p] * __expf(max_logits[base + p] - m);
+#pragma unroll
+  for (uint32_t o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+  if ((tid & 31u) == 0) red[tid >> 5] = wsum;
+  __syncthreads();
+  wsum = red[0] + red[1] + red[2] + red[3];
+  const float inv_w = (wsum > 0.f) ? 1.f / wsum : 0.f;
+
+  const uint32_t row = tid / LANES_PER_ROW;
+  const uint32_t col = (tid % LANES_PER_ROW) * 4;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  for (uint32_t p = row; p < np; p += ROWS) {
+    const float w = exp_sums[base + p] * __expf(max_logits[base + p] - m) * inv_w;
+    const uint2 raw = *reinterpret_cast<const uint2 *>(tmp_out + (base + p) * D + col);
+    const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+    const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+    a0 += w * v01.x;
+    a1 += w * v01.y;
+    a2 += w * v23.x;
+    a3 += w * v23.y;
+  }
+  part[row][col] = a0;
+  part[row][col + 1] = a1;
+  part[row][col + 2] = a2;
+  part[row][col + 3] = a3;
+  __syncthreads();
+  if (tid < D) {
+    float s = 0.f;
+#pragma unroll
+    for (uint32_t r = 0; r < ROWS; ++r) s += part[r][tid];
+    orow[tid] = __float2half_rn(s);
+  }
+}
+
+} // namespace pa

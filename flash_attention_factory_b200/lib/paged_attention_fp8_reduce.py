@@ -1,0 +1,36 @@
+"""``paged_attention_fp8_reduce.run``: FP8 KV cache, split-context (attention + merge kernel).
+
+Drop-in for the reference extension module of the same name
+(paged_attention_fp8_reduce/paged_attention_fp8_reduce.cpp:21-39,84-86); same 18 positional
+arguments (``fp8_scale`` after ``sm_scale``).  The cache format follows the tensor
+dtype: ``float8_e5m2`` or plain ``uint8`` mean e5m2 (what the reference binding fixes),
+``float8_e4m3fn`` means e4m3.
+"""
+from __future__ import annotations
+
+from . import _shim
+
+_ENTRY = "launch_kernels_fp8_reduce"
+
+
+def run(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
+        block_tables, context_lens, num_queries_per_tokens, sm_scale, fp8_scale, block_size,
+        max_context_len, alibi_slopes, sinks, softcap):
+    p = _shim.build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
+                           value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
+                           fp8_scale, block_size, max_context_len, alibi_slopes, sinks, softcap,
+                           fp8=True)
+    _shim.check_scratch(p, max_logits, exp_sums, tem_output)
+    return _shim.run_entry(_ENTRY, p, query.device)
+
+
+def enqueue(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
+            block_tables, context_lens, num_queries_per_tokens, sm_scale, fp8_scale, block_size,
+            max_context_len, alibi_slopes, sinks, softcap):
+    """Same arguments as ``run`` but asynchronous on the current stream (returns nothing)."""
+    p = _shim.build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
+                           value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
+                           fp8_scale, block_size, max_context_len, alibi_slopes, sinks, softcap,
+                           fp8=True)
+    _shim.check_scratch(p, max_logits, exp_sums, tem_output)
+    _shim.enqueue_entry(_ENTRY, p, query.device)

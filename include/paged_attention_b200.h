@@ -1,0 +1,162 @@
+/*
+ * paged_attention_b200.h -- C ABI of the B200 paged-attention decode library
+ * (libpaged_attention_b200.so).
+ *
+ * The four launch_kernels_* entry points replace, one for one, the four host
+ * launchers of baodii/flash_attention_factory; each takes exactly the
+ * quantities the reference's pybind shims unpack from their torch tensors
+ * (paged_attention_loop/paged_attention_loop.cpp:44-79) and passes them in one
+ * plain struct.  No torch types, no C++ types and no exceptions cross this
+ * boundary: every function returns a pa_status code and the message of the
+ * last failure on the calling thread is available from pa_last_error().
+ *
+ * Memory contract (same as the reference): every buffer is allocated and owned
+ * by the caller and lives on the current CUDA device; the library allocates
+ * nothing on the device and keeps no per-call state.
+ *
+ * Data layouts (reference paged_attention_kernel_loop.hpp:44-62):
+ *   query        fp16  [num_seqs, num_heads, head_size]
+ *   key_cache    fp16 or 1-byte FP8  [num_blocks, block_size, num_kv_heads, head_size]
+ *   value_cache  same layout and type as key_cache
+ *   block_tables int32 (read as uint32) [num_seqs, max_blocks_per_seq]
+ *   context_lens int32 (read as uint32) [num_seqs]
+ *   out          fp16  [num_seqs, num_heads, head_size]
+ *   max_logits   fp32  [num_seqs, num_heads, max_num_partitions]       (reduce only)
+ *   exp_sums     fp32  [num_seqs, num_heads, max_num_partitions]       (reduce only)
+ *   tmp_out      fp16  [num_seqs, num_heads, max_num_partitions, head_size] (reduce only)
+ *   sinks        fp16  [num_heads] or NULL
+ */
+#ifndef PAGED_ATTENTION_B200_H_
+#define PAGED_ATTENTION_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PA_API __attribute__((visibility("default")))
+
+typedef enum pa_status {
+  PA_OK = 0,
+  /* (head_size, block_size) or num_queries_per_tokens outside the supported
+   * set; the message strings are the reference's own
+   * (paged_attention_loop/launch_kernels_loop.h:114-115,170-172). */
+  PA_ERR_UNSUPPORTED = 1,
+  PA_ERR_BAD_ARG = 2, /* null pointer, inconsistent sizes, misaligned buffer */
+  PA_ERR_CUDA = 3,    /* a CUDA runtime / driver call failed */
+  PA_ERR_TIMEOUT = 4  /* a bounded device-side wait gave up (see pa_device_status) */
+} pa_status;
+
+typedef enum pa_kv_dtype {
+  PA_KV_F16 = 0,
+  PA_KV_FP8_E5M2 = 1, /* the format the reference bindings hard-wire
+                         (paged_attention_fp8_loop/paged_attention_fp8_loop.cpp:43) */
+  PA_KV_FP8_E4M3 = 2  /* e4m3fn bit layout (no infinities, 0x7F/0xFF = NaN) */
+} pa_kv_dtype;
+
+typedef struct pa_params {
+  /* outputs */
+  void *out;          /* fp16 [num_seqs, num_heads, head_size] */
+  float *max_logits;  /* reduce: written for partitions < ceil(ctx/partition_size) */
+  float *exp_sums;    /* reduce: same indexing as max_logits */
+  void *tmp_out;      /* reduce: fp16 per-partition normalised partial outputs */
+  /* inputs */
+  const void *query;
+  const void *key_cache;
+  const void *value_cache;
+  const void *sinks;             /* nullable */
+  const uint32_t *block_tables;
+  const uint32_t *context_lens;
+  /* sizes: the values the reference reads from tensor shapes
+   * (paged_attention_loop/paged_attention_loop.cpp:60-65) */
+  uint32_t num_seqs;               /* query.size(0) */
+  uint32_t num_heads;              /* query.size(1) */
+  uint32_t head_size;              /* query.size(2): 128 or 64 */
+  uint32_t num_kv_heads;           /* key_cache.size(2) */
+  uint32_t max_num_partitions;     /* max_logits.size(2); stride of the reduce scratch */
+  uint32_t max_blocks_per_seq;     /* block_tables.size(1) */
+  uint32_t block_size;             /* tokens per KV block: 16, 32, 64 or 128 */
+  uint32_t num_queries_per_tokens; /* GQA group, 1..8; must equal num_heads / num_kv_heads */
+  uint32_t max_context_len;        /* scheduling hint only (the reference ignores it); 0 = unknown */
+  uint32_t reserved0;
+  uint64_t num_blocks;             /* key_cache.size(0); bounds the TMA descriptor, so a
+                                      block id >= num_blocks reads zeros instead of faulting */
+  float sm_scale;
+  float fp8_scale; /* per-tensor dequantisation scale of an FP8 cache; ignored for fp16 */
+  int32_t kv_dtype; /* pa_kv_dtype; must match the entry point (fp16 vs FP8) */
+  int32_t reserved1;
+} pa_params;
+
+/* Tiling knobs of include/paged_attention_policy_v2.hpp for one
+ * (head_size, block_size, group) triple, as run-time values. */
+typedef struct pa_policy_info {
+  uint32_t partition_size;        /* tokens per partition of the reduce variant */
+  uint32_t stages;                /* base policy pipeline depth of the reference (3) */
+  uint32_t head_size_stride;      /* reference MMA k-slice (16) */
+  uint32_t partition_stride;      /* merge kernel: partitions per step (8) */
+  uint32_t max_partitions_per_sg; /* reference merge-kernel register rows */
+  uint32_t tokens_per_stage;      /* this library: tokens per shared-memory ring stage */
+  uint32_t ring_stages;           /* this library: TMA ring depth for the fp16 cache */
+  uint32_t ring_stages_fp8;       /* this library: TMA ring depth for an FP8 cache */
+  uint32_t consumer_warps;        /* MMA warps per CTA (one more warp issues TMA) */
+  uint32_t threads_per_cta;
+} pa_policy_info;
+
+/*
+ * The four launchers.  `stream` is a cudaStream_t (NULL = default stream) of
+ * the current device.  If `us_out` is NULL the call is asynchronous: kernels
+ * are only enqueued.  If `us_out` is non-NULL the call blocks until the work
+ * is done and stores device execution time in microseconds, reproducing the
+ * reference's blocking launch-and-profile behaviour
+ * (paged_attention_loop/launch_kernels_loop.h:32-34,51-53).
+ */
+
+/* fp16 KV cache, single pass.  Replaces dispatch_paged_attention_loop +
+ * launch_paged_attn_loop (paged_attention_loop/launch_kernels_loop.h:16-54,56-173).
+ * Writes `out` only; max_logits / exp_sums / tmp_out are accepted and unused, as
+ * in the reference.  us_out[0] = kernel time. */
+PA_API int launch_kernels_loop(const pa_params *p, void *stream, float *us_out);
+
+/* fp16 KV cache, split-context: attention kernel per 512-token (256 for
+ * head_size 64) partition + merge kernel.  Replaces dispatch_paged_attention +
+ * launch_paged_attn_v2 (paged_attention_reduce/launch_kernels_reduce.h:18-78,80-197).
+ * us_out[0] = attention kernel, us_out[1] = merge kernel. */
+PA_API int launch_kernels_reduce(const pa_params *p, void *stream, float *us_out);
+
+/* FP8 KV cache, single pass.  Replaces dispatch_paged_attention_fp8_loop +
+ * launch_paged_attn_fp8_loop
+ * (paged_attention_fp8_loop/launch_kernels_fp8_loop.h:17-56,58-175). */
+PA_API int launch_kernels_fp8_loop(const pa_params *p, void *stream, float *us_out);
+
+/* FP8 KV cache, split-context.  Replaces dispatch_paged_attention_fp8 +
+ * launch_paged_attn_fp8_v2
+ * (paged_attention_fp8_reduce/launch_kernels_fp8_reduce.h:16-76,78-196). */
+PA_API int launch_kernels_fp8_reduce(const pa_params *p, void *stream, float *us_out);
+
+/* Compile-time policy of include/paged_attention_policy_v2.hpp as data
+ * (reference include/paged_attention_policy_v2.hpp:5-100).  Returns
+ * PA_ERR_UNSUPPORTED for triples the launchers reject. */
+PA_API int pa_query_policy(uint32_t head_size, uint32_t block_size, uint32_t group,
+                           pa_policy_info *info);
+
+/* Partition size the reduce variant uses for a head size (512 / 256), i.e. the
+ * divisor callers use to size max_logits / exp_sums / tmp_out; 0 if unsupported. */
+PA_API uint32_t pa_partition_size(uint32_t head_size);
+
+/* Message of the last non-PA_OK return on the calling thread ("" if none). */
+PA_API const char *pa_last_error(void);
+
+/* Reads (and clears) the device status word of the current device: 0 if no
+ * kernel of this library ever gave up a bounded wait, else PA_ERR_TIMEOUT.
+ * Synchronises the device. */
+PA_API int pa_device_status(void);
+
+/* Library version, "major.minor". */
+PA_API const char *pa_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PAGED_ATTENTION_B200_H_ */

@@ -1,0 +1,121 @@
+"""Bit-exact checks of block-table indexing and partition bookkeeping (run on a B200)."""
+import pytest
+import torch
+
+from _util import make_case, run_entry
+from oracle import paged_attention_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def one_hot_value_case(kv_dtype, block_size, ctx, head_size=128, seed=0):
+    """K = 0 (uniform softmax), V[token t] = one-hot at dim (t % head_size) times 2^(t // head_size):
+    out[d] * ctx is then an exact integer code of WHICH tokens were read."""
+    c = make_case(seed=seed, num_seqs=len(ctx), num_heads=2, num_kv_heads=1, head_size=head_size,
+                  block_size=block_size, context_lens=ctx, kv_dtype="float16", extra_blocks=5)
+    c["key_cache"].zero_()
+    v = c["value_cache"]
+    v.fill_(3.0)  # unread rows would show up as 3s
+    for i, n in enumerate(ctx):
+        for t in range(n):
+            blk = int(c["block_tables"][i, t // block_size])
+            row = v[blk, t % block_size, 0]
+            row.zero_()
+            row[t % head_size] = 2.0 ** (t // head_size)
+    if kv_dtype != "float16":
+        dt = {"float8_e5m2": torch.float8_e5m2, "float8_e4m3fn": torch.float8_e4m3fn}[kv_dtype]
+        c["key_cache"] = c["key_cache"].to(dt)
+        c["value_cache"] = c["value_cache"].to(dt)
+        c["kv_dtype"] = kv_dtype
+    return c
+
+
+@pytest.mark.parametrize("kv", ["float16", "float8_e5m2", "float8_e4m3fn"])
+@pytest.mark.parametrize("block_size,ctx", [(16, [128, 64, 256]), (64, [512, 128]), (32, [1024])])
+@pytest.mark.parametrize("variant", ["loop", "reduce"])
+def test_every_token_is_read_exactly_once(cuda_device, kv, block_size, ctx, variant):
+    # ctx values are powers of two, so 1/ctx and every partial sum are exact in fp16/fp32
+    c = one_hot_value_case(kv, block_size, ctx)
+    res = run_entry(variant, c, cuda_device)
+    for i, n in enumerate(ctx):
+        expect = torch.zeros(128)
+        for t in range(n):
+            expect[t % 128] += 2.0 ** (t // 128)
+        expect = (expect / n).to(torch.float16)
+        for h in range(2):
+            assert torch.equal(res["out"][i, h], expect), f"seq {i} head {h}"
+
+
+@pytest.mark.parametrize("variant", ["loop", "reduce"])
+def test_block_table_permutation_does_not_change_the_result(cuda_device, variant):
+    c = make_case(seed=21, num_seqs=3, num_heads=8, num_kv_heads=2, head_size=128, block_size=16,
+                  context_lens=[700, 33, 512], kv_dtype="float8_e5m2")
+    a = run_entry(variant, c, cuda_device)["out"]
+    # move every physical block somewhere else and rewrite the table accordingly
+    nb = c["key_cache"].shape[0]
+    perm = torch.randperm(nb, generator=torch.Generator().manual_seed(1))
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(nb)
+    c2 = dict(c)
+    c2["key_cache"] = c["key_cache"].view(torch.uint8)[perm].view(torch.float8_e5m2)
+    c2["value_cache"] = c["value_cache"].view(torch.uint8)[perm].view(torch.float8_e5m2)
+    c2["block_tables"] = inv[c["block_tables"].long()].to(torch.int32)
+    b = run_entry(variant, c2, cuda_device)["out"]
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("kv", ["float16", "float8_e4m3fn"])
+def test_partition_scratch_layout_and_untouched_rows(cuda_device, kv):
+    """max_logits / exp_sums / tmp_out: rows p < ceil(ctx/P) hold the partition statistics,
+    rows p >= ceil(ctx/P) keep the caller's bytes; strides follow max_logits.size(2)."""
+    ctx = [1300, 512, 1, 513]
+    c = make_case(seed=31, num_seqs=4, num_heads=8, num_kv_heads=2, head_size=128, block_size=16,
+                  context_lens=ctx, kv_dtype=kv, sinks=True)
+    npart = 5  # larger than needed (3): the stride must come from the tensor shape
+    res = run_entry("reduce", c, cuda_device, max_num_partitions=npart, poison=-123.0)
+    ml, es, tmp, written = oracle.partition_stats_ref(
+        c["query"], c["key_cache"], c["value_cache"], c["block_tables"], c["context_lens"], 512,
+        sm_scale=c["sm_scale"], sinks=c["sinks"], fp8_scale=c["fp8_scale"], max_num_partitions=npart)
+    for i, n in enumerate(ctx):
+        k = (n + 511) // 512
+        assert written[i, :k].all()
+        # untouched: exactly the poison value
+        assert (res["max_logits"][i, :, k:] == -123.0).all()
+        assert (res["exp_sums"][i, :, k:] == -123.0).all()
+        assert (res["tmp_out"][i, :, k:] == -123.0).all()
+        torch.testing.assert_close(res["max_logits"][i, :, :k], ml[i, :, :k], atol=1e-3, rtol=1e-3)
+        torch.testing.assert_close(res["exp_sums"][i, :, :k], es[i, :, :k], atol=1e-3, rtol=1e-2)
+        torch.testing.assert_close(res["tmp_out"][i, :, :k].float(), tmp[i, :, :k], atol=1e-3, rtol=1e-2)
+    merged = oracle.merge_partitions_ref(res["max_logits"], res["exp_sums"], res["tmp_out"], ctx, 512)
+    torch.testing.assert_close(res["out"].float(), merged.float(), atol=2e-3, rtol=1e-2)
+
+
+def test_loop_leaves_the_scratch_buffers_alone(cuda_device):
+    """The loop entry point accepts max_logits / exp_sums / tem_output and never writes them
+    (launch_kernels_loop.h:39-47)."""
+    c = make_case(seed=41, num_seqs=2, num_heads=4, num_kv_heads=4, head_size=64, block_size=16,
+                  context_lens=[600, 10])
+    res = run_entry("loop", c, cuda_device, poison=55.0)
+    assert (res["max_logits"] == 55.0).all() and (res["exp_sums"] == 55.0).all()
+    assert (res["tmp_out"] == 55.0).all()
+
+
+def test_out_of_range_block_ids_read_zeros_without_faulting(cuda_device):
+    """A block id >= num_blocks is outside the TMA descriptor and reads as zeros."""
+    c = make_case(seed=51, num_seqs=1, num_heads=2, num_kv_heads=1, head_size=128, block_size=16,
+                  context_lens=[64])
+    c["block_tables"][0, 2] = 10_000
+    k = c["key_cache"].clone()
+    v = c["value_cache"].clone()
+    zero = torch.zeros(1, *k.shape[1:], dtype=k.dtype)
+    cz = dict(c)
+    cz["key_cache"] = torch.cat([k, zero])
+    cz["value_cache"] = torch.cat([v, zero])
+    cz["block_tables"] = c["block_tables"].clone()
+    cz["block_tables"][0, 2] = k.shape[0]
+    want = run_entry("loop", cz, cuda_device)["out"]
+    got = run_entry("loop", c, cuda_device)["out"]
+    assert torch.equal(got, want)
+    import flash_attention_factory_b200 as pkg
+
+    pkg.device_status()
