@@ -277,6 +277,8 @@ def main() -> None:
                     help="override the entry point the configuration names")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--num-seqs", type=int, default=None,
+                    help="override the number of sequences (small cases for profiler captures)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
 
@@ -284,6 +286,8 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     spec = config_spec(a.config)
+    if a.num_seqs is not None:
+        spec["num_seqs"] = a.num_seqs
     variant = a.variant or pick_variant(spec)
 
     if a.impl == "reference":

@@ -77,6 +77,8 @@ inline int validate_params(const pa_params *p, bool fp8_entry, bool needs_scratc
   } else if (p->kv_dtype != PA_KV_F16) {
     return fail(PA_ERR_BAD_ARG, "fp16 entry point needs kv_dtype f16, got %d", p->kv_dtype);
   }
+  if (!(p->sm_scale > 0.f) || (fp8_entry && !(p->fp8_scale > 0.f)))
+    return fail(PA_ERR_BAD_ARG, "sm_scale and fp8_scale must be positive and finite");
   if (p->num_seqs == 0) return PA_OK; // nothing to do; the launcher returns early
   if (!p->out || !p->query || !p->key_cache || !p->value_cache || !p->block_tables || !p->context_lens)
     return fail(PA_ERR_BAD_ARG, "a required pointer is null");
@@ -91,15 +93,18 @@ inline int validate_params(const pa_params *p, bool fp8_entry, bool needs_scratc
     return fail(PA_ERR_BAD_ARG, "num_seqs and num_kv_heads are limited to 65535");
   if (!aligned16(p->key_cache) || !aligned16(p->value_cache))
     return fail(PA_ERR_BAD_ARG, "key_cache / value_cache must be 16-byte aligned");
-  if ((reinterpret_cast<uintptr_t>(p->query) & 3u) || (reinterpret_cast<uintptr_t>(p->out) & 1u))
-    return fail(PA_ERR_BAD_ARG, "query / out are misaligned");
+  if (!aligned16(p->query) || !aligned16(p->out))
+    return fail(PA_ERR_BAD_ARG, "query / out must be 16-byte aligned");
+  if (static_cast<uint64_t>(p->num_seqs) * p->num_kv_heads * (needs_scratch ? p->max_num_partitions : 1u) >=
+      (1ull << 32))
+    return fail(PA_ERR_BAD_ARG, "too many work items for a 32-bit index");
   if (needs_scratch) {
     if (!p->max_logits || !p->exp_sums || !p->tmp_out)
       return fail(PA_ERR_BAD_ARG, "the reduce variant needs max_logits, exp_sums and tmp_out");
     if (p->max_num_partitions == 0 || p->max_num_partitions > 65535u)
       return fail(PA_ERR_BAD_ARG, "max_num_partitions must be in 1..65535");
-    if (reinterpret_cast<uintptr_t>(p->tmp_out) & 7u)
-      return fail(PA_ERR_BAD_ARG, "tmp_out must be 8-byte aligned");
+    if (!aligned16(p->tmp_out))
+      return fail(PA_ERR_BAD_ARG, "tmp_out must be 16-byte aligned");
   }
   return PA_OK;
 }
@@ -138,6 +143,7 @@ AttnArgs make_attn_args(const pa_params *p) {
   a.sinks = static_cast<const __half *>(p->sinks);
   a.block_tables = p->block_tables;
   a.context_lens = p->context_lens;
+  a.num_seqs = p->num_seqs;
   a.num_heads = p->num_heads;
   a.num_kv_heads = p->num_kv_heads;
   a.group = p->num_queries_per_tokens;
@@ -183,8 +189,11 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
   cfg.dynamicSmemBytes = L::DYN_SMEM;
   cfg.stream = stream;
   if (MODE == MODE_SPLIT) {
-    // kv head fastest: CTAs that run together read neighbouring rows of the same KV blocks
-    cfg.gridDim = dim3(p->num_kv_heads, p->max_num_partitions, p->num_seqs);
+    // persistent CTAs, two per SM, each walking the (seq, partition, kv head) items with
+    // stride gridDim.x; the TMA ring keeps streaming across item boundaries
+    const uint64_t items = static_cast<uint64_t>(p->num_kv_heads) * p->max_num_partitions * p->num_seqs;
+    const uint64_t resident = 2ull * static_cast<uint64_t>(dev.sm_count);
+    cfg.gridDim = dim3(static_cast<unsigned>(items < resident ? items : resident), 1, 1);
     cfg.numAttrs = 0;
   } else {
     const uint32_t cs = choose_cluster_size(p, dev.sm_count, policy::tokens_per_stage);

@@ -51,6 +51,7 @@ struct AttnArgs {
   const __half *sinks; // nullable
   const uint32_t *block_tables;
   const uint32_t *context_lens;
+  uint32_t num_seqs;
   uint32_t num_heads;
   uint32_t num_kv_heads;
   uint32_t group;
@@ -59,7 +60,7 @@ struct AttnArgs {
   uint32_t block_shift;     // log2(block_size)
   uint32_t rows_per_box;    // min(block_size, tokens_per_stage)
   uint32_t boxes_per_stage; // tokens_per_stage / rows_per_box
-  float scale_log2;         // sm_scale * fp8_scale * log2(e)
+  float scale_log2;         // sm_scale * fp8_scale * log2(e), > 0
   float out_scale;          // fp8_scale (1 for fp16)
 };
 
@@ -73,16 +74,21 @@ struct SmemLayout {
   static constexpr uint32_t NW = policy::consumer_warps;
   static constexpr uint32_t TS = policy::tokens_per_stage;
   static constexpr uint32_t NSTAGES = policy::ring_stages;
-  static constexpr uint32_t SLAB_TILE = TS * geo::slab_bytes;         // one slab of one stage
-  static constexpr uint32_t KV_TILE = geo::num_slabs * SLAB_TILE;     // K (or V) of one stage
+  static constexpr uint32_t SLAB_TILE = TS * geo::slab_bytes;     // one slab of one stage
+  static constexpr uint32_t KV_TILE = geo::num_slabs * SLAB_TILE; // K (or V) of one stage
   static constexpr uint32_t STAGE_BYTES = 2 * KV_TILE;
   static constexpr uint32_t RING_BYTES = NSTAGES * STAGE_BYTES;
-  // merge scratch, aliased on the ring once every stage has been consumed
-  static constexpr uint32_t WARP_AREA_FLOATS = 8 * D + 16; // O[8][D], m[8], l[8]
-  static constexpr uint32_t MERGE_BYTES = (NW + 1) * WARP_AREA_FLOATS * 4;
-  static_assert(MERGE_BYTES <= RING_BYTES, "merge scratch must fit in the ring");
-  static constexpr uint32_t BAR_OFFSET = RING_BYTES;
-  static constexpr uint32_t TOTAL_BYTES = RING_BYTES + 2 * NSTAGES * 8 + 16;
+  // merge scratch after the ring: two O[8][D] buffers that the consumer warps fill in a
+  // fixed order (warps 0,1 store, warps 2,3 add: the result does not depend on timing),
+  // per-warp (max, sum) of the 8 query columns, and the CTA's merged (max, sum)
+  static_assert(NW == 4, "the two-round merge below is written for four consumer warps");
+  static constexpr uint32_t OACC_OFFSET = RING_BYTES;
+  static constexpr uint32_t OACC_BYTES = 2 * 8 * D * 4;
+  static constexpr uint32_t WARP_ML_OFFSET = OACC_OFFSET + OACC_BYTES; // m[NW][8], l[NW][8]
+  static constexpr uint32_t WARP_ML_BYTES = 2 * 2 * NW * 8 * 4; // double-buffered by item parity
+  static constexpr uint32_t CTA_ML_OFFSET = WARP_ML_OFFSET + WARP_ML_BYTES; // M[8], L[8]
+  static constexpr uint32_t BAR_OFFSET = CTA_ML_OFFSET + 64;
+  static constexpr uint32_t TOTAL_BYTES = BAR_OFFSET + 2 * NSTAGES * 8 + 16;
   static constexpr uint32_t DYN_SMEM = TOTAL_BYTES + 1024; // slack for 1024-byte alignment
 };
 
@@ -97,6 +103,72 @@ __device__ __forceinline__ uint32_t acc_dim_index(uint32_t tile, uint32_t h, uin
   }
 }
 
+// One unit of work of a CTA: tokens [tok_begin, tok_end) of (seq, kv_head).
+struct WorkItem {
+  uint32_t linear; // position in the dense (seq, partition, kv_head) enumeration (split mode)
+  uint32_t seq, kv_head, partition;
+  uint32_t tok_begin, tok_end;
+  bool valid;
+};
+
+// Split mode: CTA b handles the items b, b + gridDim.x, ... of the dense enumeration with
+// the KV head fastest (CTAs that run together stream neighbouring rows of the same KV
+// blocks); partitions that start at or past the context are skipped and their scratch rows
+// stay untouched (reference paged_attention_kernel_v2.hpp:194-200,577-579).
+template <uint32_t PARTITION>
+__device__ __forceinline__ WorkItem find_split_item(uint32_t linear, const AttnArgs &args) {
+  WorkItem it{};
+  const uint32_t hk = args.num_kv_heads;
+  const uint32_t per_seq = hk * args.max_num_partitions;
+  const uint32_t total = per_seq * args.num_seqs;
+  it.valid = false;
+  while (linear < total) {
+    const uint32_t seq = linear / per_seq;
+    const uint32_t rem = linear - seq * per_seq;
+    const uint32_t part = rem / hk;
+    const uint32_t ctx = __ldg(args.context_lens + seq);
+    if (part * PARTITION < ctx) {
+      it.linear = linear;
+      it.seq = seq;
+      it.kv_head = rem - part * hk;
+      it.partition = part;
+      it.tok_begin = part * PARTITION;
+      it.tok_end = min(ctx, it.tok_begin + PARTITION);
+      it.valid = true;
+      return it;
+    }
+    linear += gridDim.x;
+  }
+  return it;
+}
+
+template <int D, int KV>
+__device__ __forceinline__ void load_q_fragments(uint32_t (&qf)[D / 16][2], const AttnArgs &args,
+                                                 const WorkItem &it, uint32_t gid, uint32_t t4) {
+  // B operand of S^T = K . Q^T: column n = gid is the query head inside the group
+  const uint32_t G = args.group;
+  const __half *qrow =
+      args.query + (static_cast<size_t>(it.seq) * args.num_heads + it.kv_head * G + gid) * D;
+#pragma unroll
+  for (uint32_t ks = 0; ks < D / 16; ++ks) {
+    if (gid < G) {
+      if constexpr (KV == KV_F16) {
+        qf[ks][0] = __ldg(reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 2 * t4));
+        qf[ks][1] = __ldg(reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 8 + 2 * t4));
+      } else {
+        // FP8 K fragments take 4 consecutive bytes per lane, so the k slots of an MMA
+        // step map to dims 16*ks + 4*t4 + {0,1} and + {2,3}
+        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(qrow + ks * 16 + 4 * t4));
+        qf[ks][0] = v.x;
+        qf[ks][1] = v.y;
+      }
+    } else {
+      qf[ks][0] = 0u;
+      qf[ks][1] = 0u;
+    }
+  }
+}
+
 template <int D, int KV, int MODE>
 __global__ void __launch_bounds__(paged_attention_policy_v2<D, KV>::threads_per_cta, 2)
 paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
@@ -108,12 +180,16 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   constexpr uint32_t TS = L::TS;
   constexpr uint32_t NSTAGES = L::NSTAGES;
   constexpr uint32_t KSTEPS = D / 16; // MMA k-steps of QK^T == accumulator tiles of PV
+  constexpr uint32_t NCONS = NW * 32; // consumer threads
 
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment of the ring makes the TMA swizzle a function of (row, chunk).
   // The offset is identical in every CTA, so cluster-mapped addresses line up.
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t *smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  float *o_acc = reinterpret_cast<float *>(smem + L::OACC_OFFSET);
+  float *warp_ml = reinterpret_cast<float *>(smem + L::WARP_ML_OFFSET); // [2][m|l][NW][8]
+  float *cta_ml = reinterpret_cast<float *>(smem + L::CTA_ML_OFFSET);  // M[8], L[8]
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + L::BAR_OFFSET);
   uint64_t *empty_bar = full_bar + NSTAGES;
   volatile uint32_t *abort_flag =
@@ -122,34 +198,27 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
 
-  // ---- which tokens does this CTA own? (integer bookkeeping, bit-exact)
-  uint32_t seq, kv_head, partition = 0, cta_rank = 0, num_ranks = 1;
+  // ---- the first work item of this CTA (integer bookkeeping, bit-exact)
+  uint32_t cta_rank = 0, num_ranks = 1;
+  WorkItem first{};
   if constexpr (MODE == MODE_SPLIT) {
-    kv_head = blockIdx.x;
-    partition = blockIdx.y;
-    seq = blockIdx.z;
+    first = find_split_item<policy::partition_size>(blockIdx.x, args);
   } else {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     cta_rank = cluster.block_rank();
     num_ranks = cluster.num_blocks();
-    kv_head = blockIdx.y;
-    seq = blockIdx.z;
-  }
-  const uint32_t ctx = args.context_lens[seq];
-  uint32_t tok_begin, tok_end;
-  if constexpr (MODE == MODE_SPLIT) {
-    tok_begin = partition * policy::partition_size;
-    if (tok_begin >= ctx) return; // partition past the context: scratch rows stay untouched
-    tok_end = min(ctx, tok_begin + policy::partition_size);
-  } else {
+    first.seq = blockIdx.z;
+    first.kv_head = blockIdx.y;
+    first.partition = 0;
+    const uint32_t ctx = args.context_lens[first.seq];
+    // the context is cut into whole stages, spread evenly over the CTAs of the cluster
     const uint32_t total_stages = divide_round_up(ctx, TS);
     const uint32_t stages_per_rank = divide_round_up(total_stages, num_ranks);
-    tok_begin = min(ctx, cta_rank * stages_per_rank * TS);
-    tok_end = min(ctx, (cta_rank + 1) * stages_per_rank * TS);
+    first.tok_begin = min(ctx, cta_rank * stages_per_rank * TS);
+    first.tok_end = min(ctx, (cta_rank + 1) * stages_per_rank * TS);
+    first.valid = true;
   }
-  const uint32_t my_tokens = tok_end - tok_begin;
-  const uint32_t my_stages = divide_round_up(my_tokens, TS);
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < NSTAGES; ++s) {
@@ -169,54 +238,67 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
     const uint32_t rows = args.rows_per_box;
     const uint32_t bps = args.boxes_per_stage;
-    const uint32_t total_boxes = divide_round_up(my_tokens, rows);
-    const uint32_t *table = args.block_tables + static_cast<size_t>(seq) * args.max_blocks_per_seq;
     const uint32_t box_bytes = rows * geo::row_bytes; // K (or V) bytes of one box
     const uint32_t ring_base = smem_u32(smem);
-    const int32_t x0 = static_cast<int32_t>(kv_head * D);
+    const uint32_t row_mask = (1u << args.block_shift) - 1u;
+    uint32_t slot = 0, phase = 0; // ring position, continuous across work items
     bool alive = true;
 
-    auto fetch_block_id = [&](uint32_t box) -> uint32_t {
-      if (box >= total_boxes) return 0u;
-      const uint32_t tok = tok_begin + box * rows;
-      return __ldg(table + (tok >> args.block_shift));
+    auto fetch_block_id = [&](const WorkItem &it, uint32_t box) -> uint32_t {
+      const uint32_t tok = it.tok_begin + box * rows;
+      if (!it.valid || tok >= it.tok_end) return 0u;
+      return __ldg(args.block_tables + static_cast<size_t>(it.seq) * args.max_blocks_per_seq +
+                   (tok >> args.block_shift));
     };
-    uint32_t block_id_next = fetch_block_id(lane);
-    for (uint32_t batch0 = 0; batch0 < total_boxes && alive; batch0 += 32) {
-      const uint32_t box = batch0 + lane;
-      const uint32_t block_id = block_id_next;
-      block_id_next = fetch_block_id(box + 32); // prefetch the next batch of table entries
-      const bool valid = box < total_boxes;
-      const uint32_t tok = tok_begin + box * rows;
-      const int32_t y = static_cast<int32_t>((block_id << args.block_shift) +
-                                             (tok & ((1u << args.block_shift) - 1u)));
-      const uint32_t first_stage = batch0 / bps;
-      const uint32_t last_box = min(batch0 + 31u, total_boxes - 1u);
-      const uint32_t last_stage = last_box / bps;
-      for (uint32_t st = first_stage; st <= last_stage; ++st) {
-        const uint32_t slot = st % NSTAGES;
-        const uint32_t phase = (st / NSTAGES) & 1u;
-        if (lane == 0) {
-          alive = mbar_wait_bounded(&empty_bar[slot], phase ^ 1u, abort_flag);
-          if (alive) {
-            const uint32_t boxes_here = min(bps, total_boxes - st * bps);
-            mbar_arrive_expect_tx(&full_bar[slot], boxes_here * box_bytes * 2u);
+
+    WorkItem cur = first;
+    uint32_t block_id_next = fetch_block_id(cur, lane);
+    while (cur.valid && alive) {
+      WorkItem nxt{};
+      nxt.valid = false;
+      if constexpr (MODE == MODE_SPLIT)
+        nxt = find_split_item<policy::partition_size>(cur.linear + gridDim.x, args);
+      const uint32_t total_boxes = divide_round_up(cur.tok_end - cur.tok_begin, rows);
+      const int32_t x0 = static_cast<int32_t>(cur.kv_head * D);
+      for (uint32_t batch0 = 0; batch0 < total_boxes && alive; batch0 += 32) {
+        const uint32_t box = batch0 + lane;
+        const uint32_t block_id = block_id_next;
+        // prefetch the table entries of the next batch (of this item or of the next one)
+        block_id_next = (batch0 + 32 < total_boxes) ? fetch_block_id(cur, box + 32)
+                                                    : fetch_block_id(nxt, lane);
+        const bool valid = box < total_boxes;
+        const uint32_t tok = cur.tok_begin + box * rows;
+        const int32_t y = static_cast<int32_t>((block_id << args.block_shift) + (tok & row_mask));
+        const uint32_t boxes_in_batch = min(32u, total_boxes - batch0);
+        const uint32_t stages_in_batch = divide_round_up(boxes_in_batch, bps);
+        for (uint32_t sb = 0; sb < stages_in_batch; ++sb) {
+          if (lane == 0) {
+            alive = mbar_wait_bounded(&empty_bar[slot], phase ^ 1u, abort_flag);
+            if (alive) {
+              const uint32_t boxes_here = min(bps, boxes_in_batch - sb * bps);
+              mbar_arrive_expect_tx(&full_bar[slot], boxes_here * box_bytes * 2u);
+            }
           }
-        }
-        alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
-        if (!alive) break;
-        if (valid && box / bps == st) {
-          const uint32_t row0 = (box % bps) * rows;
-          const uint32_t stage_base = ring_base + slot * L::STAGE_BYTES;
+          alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+          if (!alive) break;
+          if (valid && lane / bps == sb) {
+            const uint32_t row0 = (lane % bps) * rows;
+            const uint32_t stage_base = ring_base + slot * L::STAGE_BYTES;
 #pragma unroll
-          for (uint32_t sl = 0; sl < geo::num_slabs; ++sl) {
-            const uint32_t dst = stage_base + sl * L::SLAB_TILE + row0 * geo::slab_bytes;
-            const int32_t x = x0 + static_cast<int32_t>(sl * geo::slab_elems);
-            tma_load_2d(dst, &tmap_k, &full_bar[slot], x, y);
-            tma_load_2d(dst + L::KV_TILE, &tmap_v, &full_bar[slot], x, y);
+            for (uint32_t sl = 0; sl < geo::num_slabs; ++sl) {
+              const uint32_t dst = stage_base + sl * L::SLAB_TILE + row0 * geo::slab_bytes;
+              const int32_t x = x0 + static_cast<int32_t>(sl * geo::slab_elems);
+              tma_load_2d(dst, &tmap_k, &full_bar[slot], x, y);
+              tma_load_2d(dst + L::KV_TILE, &tmap_v, &full_bar[slot], x, y);
+            }
+          }
+          if (++slot == NSTAGES) {
+            slot = 0;
+            phase ^= 1u;
           }
         }
       }
+      cur = nxt;
     }
   } else {
     // =========================== consumer warps ==========================
@@ -224,266 +306,295 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t gid = lane >> 2;
     const uint32_t t4 = lane & 3u;
     const uint32_t G = args.group;
+    const uint32_t ctid = threadIdx.x - 32; // 0 .. NCONS-1
+    const float scale = args.scale_log2;
 
-    // Q fragments (B operand, n = gid is the query head inside the group)
-    uint32_t qf[KSTEPS][2];
-    {
-      const __half *qrow = args.query +
-                           (static_cast<size_t>(seq) * args.num_heads + kv_head * G + gid) * D;
-#pragma unroll
-      for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
-        if (gid < G) {
-          if constexpr (KV == KV_F16) {
-            qf[ks][0] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 2 * t4);
-            qf[ks][1] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 8 + 2 * t4);
-          } else {
-            // FP8 K fragments take 4 consecutive bytes per lane, so the k slots of
-            // an MMA step map to dims 16*ks + 4*t4 + {0,1} and + {2,3}
-            qf[ks][0] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 4 * t4);
-            qf[ks][1] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 4 * t4 + 2);
-          }
-        } else {
-          qf[ks][0] = 0u;
-          qf[ks][1] = 0u;
-        }
-      }
-    }
-
-    // running softmax state of columns g = 2*t4 and 2*t4+1, in the log2 domain
-    float m_run[2] = {neg_infinity(), neg_infinity()};
-    float l_run[2] = {0.f, 0.f}; // per-lane partial sums; reduced over gid at the end
-    float acc[KSTEPS][4];
-#pragma unroll
-    for (uint32_t i = 0; i < KSTEPS; ++i) {
-      acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    }
-    // The sink is one extra logit with a zero value vector, attached to the first
-    // tokens of the context only (reference paged_attention_kernel_loop.hpp:387-401).
-    if (args.sinks != nullptr && cw == 0 && tok_begin == 0) {
-#pragma unroll
-      for (uint32_t j = 0; j < 2; ++j) {
-        const uint32_t g = 2 * t4 + j;
-        if (g < G) {
-          m_run[j] = __half2float(args.sinks[kv_head * G + g]) * kLog2e;
-          l_run[j] = (gid == 0) ? 1.f : 0.f;
-        }
-      }
-    }
-
+    // lane-dependent, stage-independent parts of the ldmatrix addresses; the chunk pair
+    // 2k, 2k+1 of a slab is reached by XOR-ing (k << 5) into the address
     const uint32_t ring_base = smem_u32(smem);
-    // lane-dependent parts of the ldmatrix addresses
-    const uint32_t lm_row_k = cw * 16 + (lane & 7u) + ((lane >> 3) & 1u) * 8u; // K, and FP8 V
-    const uint32_t lm_chunk_k = lane >> 4;
-    const uint32_t lm_row_v = cw * 16 + (lane & 7u) + (lane >> 4) * 8u; // fp16 V (transposed)
-    const uint32_t lm_chunk_v = (lane >> 3) & 1u;
+    const uint32_t lm_row_a = cw * 16 + (lane & 7u) + ((lane >> 3) & 1u) * 8u;
+    const uint32_t lm_off_a = swizzled_offset<geo::slab_bytes>(lm_row_a, lane >> 4); // K, FP8 V
+    const uint32_t lm_row_b = cw * 16 + (lane & 7u) + (lane >> 4) * 8u;
+    const uint32_t lm_off_b = swizzled_offset<geo::slab_bytes>(lm_row_b, (lane >> 3) & 1u); // fp16 V
+    constexpr uint32_t PAIRS_PER_SLAB = geo::chunks_per_slab / 2;
 
+    uint32_t slot = 0, phase = 0, item_parity = 0;
     bool alive = true;
-    for (uint32_t st = 0; st < my_stages && alive; ++st) {
-      const uint32_t slot = st % NSTAGES;
-      const uint32_t phase = (st / NSTAGES) & 1u;
-      alive = mbar_wait_bounded(&full_bar[slot], phase, abort_flag);
-      if (!alive) break;
-      const uint32_t stage_tok0 = st * TS + cw * 16; // first token of this warp's slice
-      if (stage_tok0 < my_tokens) {
-        const uint32_t n_valid = min(16u, my_tokens - stage_tok0);
-        const uint32_t k_base = ring_base + slot * L::STAGE_BYTES;
-        const uint32_t v_base = k_base + L::KV_TILE;
+    uint32_t qf[KSTEPS][2];
+    WorkItem cur = first;
+    if (cur.valid) load_q_fragments<D, KV>(qf, args, cur, gid, t4);
 
-        // ---- S^T = K . Q^T  (two accumulation chains to shorten the dependency)
-        float s_a[4] = {0.f, 0.f, 0.f, 0.f};
-        float s_b[4] = {0.f, 0.f, 0.f, 0.f};
-        if constexpr (KV == KV_F16) {
+    while (cur.valid) {
+      WorkItem nxt{};
+      nxt.valid = false;
+      if constexpr (MODE == MODE_SPLIT)
+        nxt = find_split_item<policy::partition_size>(cur.linear + gridDim.x, args);
+
+      // running softmax state of columns g = 2*t4 and 2*t4+1, in the log2 domain
+      float m_run[2] = {neg_infinity(), neg_infinity()};
+      float l_run[2] = {0.f, 0.f}; // per-lane partial sums; reduced over gid at the end
+      float acc[KSTEPS][4];
 #pragma unroll
-          for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
-            constexpr uint32_t steps_per_slab = geo::chunks_per_slab / 2;
-            const uint32_t slab = ks / steps_per_slab;
-            const uint32_t chunk0 = 2 * (ks % steps_per_slab);
-            uint32_t a[4];
-            ldmatrix_x4(a, k_base + slab * L::SLAB_TILE +
-                               swizzled_offset<geo::slab_bytes>(lm_row_k, chunk0 + lm_chunk_k));
-            if (ks & 1u) mma_m16n8k16(s_b, a, qf[ks][0], qf[ks][1]);
-            else mma_m16n8k16(s_a, a, qf[ks][0], qf[ks][1]);
-          }
-        } else {
+      for (uint32_t i = 0; i < KSTEPS; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+      // The sink is one extra logit with a zero value vector, attached to the first tokens
+      // of the context only (reference paged_attention_kernel_loop.hpp:387-401).
+      if (args.sinks != nullptr && cw == 0 && cur.tok_begin == 0) {
 #pragma unroll
-          for (uint32_t q = 0; q < KSTEPS / 2; ++q) {
-            uint32_t r[4];
-            ldmatrix_x4(r, k_base + swizzled_offset<geo::slab_bytes>(lm_row_k, 2 * q + lm_chunk_k));
-            uint32_t a[4];
-            a[0] = fp8_pair_to_half2<KV, 0, 1>(r[0]);
-            a[1] = fp8_pair_to_half2<KV, 0, 1>(r[1]);
-            a[2] = fp8_pair_to_half2<KV, 2, 3>(r[0]);
-            a[3] = fp8_pair_to_half2<KV, 2, 3>(r[1]);
-            mma_m16n8k16(s_a, a, qf[2 * q][0], qf[2 * q][1]);
-            a[0] = fp8_pair_to_half2<KV, 0, 1>(r[2]);
-            a[1] = fp8_pair_to_half2<KV, 0, 1>(r[3]);
-            a[2] = fp8_pair_to_half2<KV, 2, 3>(r[2]);
-            a[3] = fp8_pair_to_half2<KV, 2, 3>(r[3]);
-            mma_m16n8k16(s_b, a, qf[2 * q + 1][0], qf[2 * q + 1][1]);
+        for (uint32_t j = 0; j < 2; ++j) {
+          const uint32_t g = 2 * t4 + j;
+          if (g < G) {
+            m_run[j] = __half2float(args.sinks[cur.kv_head * G + g]) * kLog2e;
+            l_run[j] = (gid == 0) ? 1.f : 0.f;
           }
         }
-        // lane holds S[tok gid][g 2t4, 2t4+1] in [0],[1] and S[tok gid+8][..] in [2],[3]
-        float s[4];
-#pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) s[j] = (s_a[j] + s_b[j]) * args.scale_log2;
-        const bool partial = n_valid < 16u;
-        if (partial) {
-          // tokens past the context never count, whatever the cache holds there
-          // (reference paged_attention_kernel_loop.hpp:323-327)
-          if (gid >= n_valid) s[0] = s[1] = neg_infinity();
-          if (gid + 8 >= n_valid) s[2] = s[3] = neg_infinity();
-        }
-        // ---- online softmax (reference paged_attention_kernel_loop.hpp:382-419)
-        const float tile_max0 = quad_column_max(fmaxf(s[0], s[2]));
-        const float tile_max1 = quad_column_max(fmaxf(s[1], s[3]));
-        const float m_new0 = fmaxf(m_run[0], tile_max0);
-        const float m_new1 = fmaxf(m_run[1], tile_max1);
-        const float r0 = fast_exp2(m_run[0] - m_new0);
-        const float r1 = fast_exp2(m_run[1] - m_new1);
-        m_run[0] = m_new0;
-        m_run[1] = m_new1;
-        const float p0 = fast_exp2(s[0] - m_new0);
-        const float p1 = fast_exp2(s[1] - m_new1);
-        const float p2 = fast_exp2(s[2] - m_new0);
-        const float p3 = fast_exp2(s[3] - m_new1);
-        l_run[0] = l_run[0] * r0 + (p0 + p2); // fp32 sum of the unrounded weights
-        l_run[1] = l_run[1] * r1 + (p1 + p3);
-#pragma unroll
-        for (uint32_t i = 0; i < KSTEPS; ++i) {
-          acc[i][0] *= r0;
-          acc[i][1] *= r1;
-          acc[i][2] *= r0;
-          acc[i][3] *= r1;
-        }
-        // P rounded to fp16 for the MMA, transposed into the B-operand layout
-        const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1)); // tokens 0..7
-        const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3)); // tokens 8..15
+      }
 
-        // masks that clear V of tokens past the context, so that 0 * garbage stays 0
-        uint32_t mask_lo = 0xffffffffu, mask_hi = 0xffffffffu;
-        if (partial) {
-          mask_lo = ((2 * t4 < n_valid) ? 0x0000ffffu : 0u) | ((2 * t4 + 1 < n_valid) ? 0xffff0000u : 0u);
-          mask_hi = ((2 * t4 + 8 < n_valid) ? 0x0000ffffu : 0u) | ((2 * t4 + 9 < n_valid) ? 0xffff0000u : 0u);
+      const uint32_t my_tokens = cur.tok_end - cur.tok_begin;
+      const uint32_t my_stages = divide_round_up(my_tokens, TS);
+      for (uint32_t st = 0; st < my_stages; ++st) {
+        // after an abort the loops keep their shape (the named barriers below need every
+        // consumer warp) but no longer wait or compute
+        if (alive) alive = mbar_wait_bounded(&full_bar[slot], phase, abort_flag);
+        const uint32_t tile_tok0 = st * TS + cw * 16; // first token of this warp's slice
+        if (alive && tile_tok0 < my_tokens) {
+          const uint32_t n_valid = min(16u, my_tokens - tile_tok0);
+          const bool partial = n_valid < 16u;
+          const uint32_t k_base = ring_base + slot * L::STAGE_BYTES;
+          const uint32_t v_base = k_base + L::KV_TILE;
+          const uint32_t k_addr = k_base + lm_off_a;
+
+          // ---- S^T = K . Q^T  (two accumulation chains shorten the dependency)
+          float s_a[4] = {0.f, 0.f, 0.f, 0.f};
+          float s_b[4] = {0.f, 0.f, 0.f, 0.f};
+          if constexpr (KV == KV_F16) {
+#pragma unroll
+            for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+              uint32_t a[4];
+              ldmatrix_x4(a, (k_addr ^ ((ks % PAIRS_PER_SLAB) << 5)) + (ks / PAIRS_PER_SLAB) * L::SLAB_TILE);
+              if (ks & 1u) mma_m16n8k16(s_b, a, qf[ks][0], qf[ks][1]);
+              else mma_m16n8k16(s_a, a, qf[ks][0], qf[ks][1]);
+            }
+          } else {
+#pragma unroll
+            for (uint32_t q = 0; q < KSTEPS / 2; ++q) {
+              // r[0]/r[1]: rows gid / gid+8 of chunk 2q, r[2]/r[3]: the same of chunk 2q+1
+              uint32_t r[4];
+              ldmatrix_x4(r, k_addr ^ (q << 5));
+              uint32_t a[4];
+              fp8x4_to_half2x2<KV>(r[0], a[0], a[2]);
+              fp8x4_to_half2x2<KV>(r[1], a[1], a[3]);
+              mma_m16n8k16(s_a, a, qf[2 * q][0], qf[2 * q][1]);
+              fp8x4_to_half2x2<KV>(r[2], a[0], a[2]);
+              fp8x4_to_half2x2<KV>(r[3], a[1], a[3]);
+              mma_m16n8k16(s_b, a, qf[2 * q + 1][0], qf[2 * q + 1][1]);
+            }
+          }
+          // lane holds S[tok gid][g 2t4, 2t4+1] in [0],[1] and S[tok gid+8][..] in [2],[3]
+          float c[4];
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) c[j] = s_a[j] + s_b[j];
+          if (partial) {
+            // tokens past the context never count, whatever the cache holds there
+            // (reference paged_attention_kernel_loop.hpp:323-327)
+            if (gid >= n_valid) c[0] = c[1] = neg_infinity();
+            if (gid + 8 >= n_valid) c[2] = c[3] = neg_infinity();
+          }
+          // ---- online softmax (reference paged_attention_kernel_loop.hpp:382-419);
+          // scale > 0, so the maximum commutes with the scaling
+          const float m_new0 = fmaxf(m_run[0], quad_column_max(fmaxf(c[0], c[2])) * scale);
+          const float m_new1 = fmaxf(m_run[1], quad_column_max(fmaxf(c[1], c[3])) * scale);
+          const float p0 = fast_exp2(fmaf(c[0], scale, -m_new0));
+          const float p1 = fast_exp2(fmaf(c[1], scale, -m_new1));
+          const float p2 = fast_exp2(fmaf(c[2], scale, -m_new0));
+          const float p3 = fast_exp2(fmaf(c[3], scale, -m_new1));
+          const bool grew = (m_new0 != m_run[0]) || (m_new1 != m_run[1]);
+          if (__any_sync(0xffffffffu, grew)) {
+            const float r0 = fast_exp2(m_run[0] - m_new0);
+            const float r1 = fast_exp2(m_run[1] - m_new1);
+            l_run[0] *= r0;
+            l_run[1] *= r1;
+#pragma unroll
+            for (uint32_t i = 0; i < KSTEPS; ++i) {
+              acc[i][0] *= r0;
+              acc[i][1] *= r1;
+              acc[i][2] *= r0;
+              acc[i][3] *= r1;
+            }
+            m_run[0] = m_new0;
+            m_run[1] = m_new1;
+          }
+          l_run[0] += p0 + p2; // fp32 sum of the unrounded weights
+          l_run[1] += p1 + p3;
+          // P rounded to fp16 for the MMA, transposed into the B-operand layout
+          const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1)); // tokens 0..7
+          const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3)); // tokens 8..15
+
+          // masks that clear V of tokens past the context, so that 0 * garbage stays 0
+          uint32_t mask_lo = 0xffffffffu, mask_hi = 0xffffffffu;
+          if (partial) {
+            mask_lo = ((2 * t4 < n_valid) ? 0x0000ffffu : 0u) | ((2 * t4 + 1 < n_valid) ? 0xffff0000u : 0u);
+            mask_hi = ((2 * t4 + 8 < n_valid) ? 0x0000ffffu : 0u) | ((2 * t4 + 9 < n_valid) ? 0xffff0000u : 0u);
+          }
+          // ---- O^T += V^T . P^T
+          if constexpr (KV == KV_F16) {
+            const uint32_t v_addr = v_base + lm_off_b;
+#pragma unroll
+            for (uint32_t i = 0; i < KSTEPS; ++i) {
+              uint32_t a[4];
+              ldmatrix_x4_trans(a, (v_addr ^ ((i % PAIRS_PER_SLAB) << 5)) + (i / PAIRS_PER_SLAB) * L::SLAB_TILE);
+              if (partial) {
+                a[0] &= mask_lo;
+                a[1] &= mask_lo;
+                a[2] &= mask_hi;
+                a[3] &= mask_hi;
+              }
+              mma_m16n8k16(acc[i], a, pb0, pb1);
+            }
+          } else {
+            const uint32_t v_addr = v_base + lm_off_a;
+#pragma unroll
+            for (uint32_t q = 0; q < KSTEPS / 2; ++q) {
+              // 16 tokens x 32 dims of bytes, read as transposed 16-bit units:
+              // r[0]: tokens 0-7 / dims 0-15, r[1]: tokens 8-15 / dims 0-15,
+              // r[2]: tokens 0-7 / dims 16-31, r[3]: tokens 8-15 / dims 16-31.
+              // Each register = {V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1]}.
+              uint32_t r[4];
+              ldmatrix_x4_trans(r, v_addr ^ (q << 5));
+              uint32_t ae[4], ao[4];
+              fp8x4_to_even_odd_half2<KV>(r[0], ae[0], ao[0]);
+              fp8x4_to_even_odd_half2<KV>(r[2], ae[1], ao[1]);
+              fp8x4_to_even_odd_half2<KV>(r[1], ae[2], ao[2]);
+              fp8x4_to_even_odd_half2<KV>(r[3], ae[3], ao[3]);
+              if (partial) {
+                ae[0] &= mask_lo;
+                ae[1] &= mask_lo;
+                ae[2] &= mask_hi;
+                ae[3] &= mask_hi;
+                ao[0] &= mask_lo;
+                ao[1] &= mask_lo;
+                ao[2] &= mask_hi;
+                ao[3] &= mask_hi;
+              }
+              mma_m16n8k16(acc[2 * q], ae, pb0, pb1);
+              mma_m16n8k16(acc[2 * q + 1], ao, pb0, pb1);
+            }
+          }
         }
-        // ---- O^T += V^T . P^T
-        if constexpr (KV == KV_F16) {
+        // this warp is done with the stage: let the producer refill it
+        __syncwarp();
+        if (alive && lane == 0) mbar_arrive(&empty_bar[slot]);
+        if (++slot == NSTAGES) {
+          slot = 0;
+          phase ^= 1u;
+        }
+      }
+
+      // Q of the next item: issued now so that the loads fly during the merge below
+      if (nxt.valid) load_q_fragments<D, KV>(qf, args, nxt, gid, t4);
+
+      // ---- merge the consumer warps of this CTA through shared memory.  The (max, sum)
+      // slots alternate between items: a warp may publish the next item's values while a
+      // slower warp still reads this item's.
+      float *warp_m = warp_ml + item_parity * (2 * NW * 8);
+      float *warp_l = warp_m + NW * 8;
+      item_parity ^= 1u;
+      l_run[0] = quad_column_sum(l_run[0]);
+      l_run[1] = quad_column_sum(l_run[1]);
+      if (gid == 0) {
+        warp_m[cw * 8 + 2 * t4] = m_run[0];
+        warp_m[cw * 8 + 2 * t4 + 1] = m_run[1];
+        warp_l[cw * 8 + 2 * t4] = l_run[0];
+        warp_l[cw * 8 + 2 * t4 + 1] = l_run[1];
+      }
+      named_barrier_sync(1, NCONS);
+      {
+        float f[2];
+#pragma unroll
+        for (uint32_t j = 0; j < 2; ++j) {
+          float m_all = neg_infinity();
+#pragma unroll
+          for (uint32_t w = 0; w < NW; ++w) m_all = fmaxf(m_all, warp_m[w * 8 + 2 * t4 + j]);
+          f[j] = (m_run[j] == neg_infinity()) ? 0.f : fast_exp2(m_run[j] - m_all);
+        }
+        // round 1: warps 0 and 1 store their rescaled accumulators into buffers 0 and 1
+        float *buf = o_acc + (cw & 1u) * (8 * D);
+        if (cw < 2) {
 #pragma unroll
           for (uint32_t i = 0; i < KSTEPS; ++i) {
-            constexpr uint32_t tiles_per_slab = geo::chunks_per_slab / 2;
-            const uint32_t slab = i / tiles_per_slab;
-            const uint32_t chunk0 = 2 * (i % tiles_per_slab);
-            uint32_t a[4];
-            ldmatrix_x4_trans(a, v_base + slab * L::SLAB_TILE +
-                                     swizzled_offset<geo::slab_bytes>(lm_row_v, chunk0 + lm_chunk_v));
-            if (partial) {
-              a[0] &= mask_lo;
-              a[1] &= mask_lo;
-              a[2] &= mask_hi;
-              a[3] &= mask_hi;
-            }
-            mma_m16n8k16(acc[i], a, pb0, pb1);
-          }
-        } else {
 #pragma unroll
-          for (uint32_t q = 0; q < KSTEPS / 2; ++q) {
-            // 16 tokens x 32 dims of bytes, read as transposed 16-bit units:
-            // r[0]: tokens 0-7 / dims 0-15, r[1]: tokens 8-15 / dims 0-15,
-            // r[2]: tokens 0-7 / dims 16-31, r[3]: tokens 8-15 / dims 16-31.
-            // Each register = {V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1]}.
-            uint32_t r[4];
-            ldmatrix_x4_trans(r, v_base + swizzled_offset<geo::slab_bytes>(lm_row_k, 2 * q + lm_chunk_k));
-            uint32_t a[4];
-            a[0] = fp8_pair_to_half2<KV, 0, 2>(r[0]);
-            a[1] = fp8_pair_to_half2<KV, 0, 2>(r[2]);
-            a[2] = fp8_pair_to_half2<KV, 0, 2>(r[1]);
-            a[3] = fp8_pair_to_half2<KV, 0, 2>(r[3]);
-            if (partial) {
-              a[0] &= mask_lo;
-              a[1] &= mask_lo;
-              a[2] &= mask_hi;
-              a[3] &= mask_hi;
+            for (uint32_t h = 0; h < 2; ++h) {
+              const uint32_t d = acc_dim_index<KV>(i, h, gid);
+              buf[(2 * t4) * D + d] = acc[i][2 * h] * f[0];
+              buf[(2 * t4 + 1) * D + d] = acc[i][2 * h + 1] * f[1];
             }
-            mma_m16n8k16(acc[2 * q], a, pb0, pb1);
-            a[0] = fp8_pair_to_half2<KV, 1, 3>(r[0]);
-            a[1] = fp8_pair_to_half2<KV, 1, 3>(r[2]);
-            a[2] = fp8_pair_to_half2<KV, 1, 3>(r[1]);
-            a[3] = fp8_pair_to_half2<KV, 1, 3>(r[3]);
-            if (partial) {
-              a[0] &= mask_lo;
-              a[1] &= mask_lo;
-              a[2] &= mask_hi;
-              a[3] &= mask_hi;
+          }
+        }
+        named_barrier_sync(1, NCONS);
+        // round 2: warps 2 and 3 add theirs (each element has exactly one writer)
+        if (cw >= 2) {
+#pragma unroll
+          for (uint32_t i = 0; i < KSTEPS; ++i) {
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h) {
+              const uint32_t d = acc_dim_index<KV>(i, h, gid);
+              buf[(2 * t4) * D + d] += acc[i][2 * h] * f[0];
+              buf[(2 * t4 + 1) * D + d] += acc[i][2 * h + 1] * f[1];
             }
-            mma_m16n8k16(acc[2 * q + 1], a, pb0, pb1);
           }
         }
       }
-      // this warp is done with the stage: let the producer refill it
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty_bar[slot]);
-    }
-
-    // ---- merge the consumer warps of this CTA through shared memory
-    // every stage has been consumed (or the CTA gave up), so the ring is free
-    named_barrier_sync(1, NW * 32);
-    float *warp_area = reinterpret_cast<float *>(smem) + cw * L::WARP_AREA_FLOATS;
-    l_run[0] = quad_column_sum(l_run[0]);
-    l_run[1] = quad_column_sum(l_run[1]);
-    if (gid == 0) {
-      warp_area[8 * D + 2 * t4] = m_run[0];
-      warp_area[8 * D + 2 * t4 + 1] = m_run[1];
-      warp_area[8 * D + 8 + 2 * t4] = l_run[0];
-      warp_area[8 * D + 8 + 2 * t4 + 1] = l_run[1];
-    }
+      named_barrier_sync(1, NCONS);
+      {
+        // thread -> (query column g, 8 consecutive dims)
+        constexpr uint32_t THREADS_PER_ROW = D / 8;
+        const uint32_t g = ctid / THREADS_PER_ROW;
+        const uint32_t d0 = (ctid % THREADS_PER_ROW) * 8;
+        const bool ok = (*abort_flag == 0u);
+        if (g < 8) {
+          float m_all = neg_infinity();
 #pragma unroll
-    for (uint32_t i = 0; i < KSTEPS; ++i) {
+          for (uint32_t w = 0; w < NW; ++w) m_all = fmaxf(m_all, warp_m[w * 8 + g]);
+          float l_all = 0.f;
 #pragma unroll
-      for (uint32_t h = 0; h < 2; ++h) {
-        const uint32_t d = acc_dim_index<KV>(i, h, gid);
-        warp_area[(2 * t4) * D + d] = acc[i][2 * h];
-        warp_area[(2 * t4 + 1) * D + d] = acc[i][2 * h + 1];
-      }
-    }
-    named_barrier_sync(1, NW * 32);
-
-    const float *areas = reinterpret_cast<const float *>(smem);
-    float *cta_area = reinterpret_cast<float *>(smem) + NW * L::WARP_AREA_FLOATS;
-    const uint32_t ctid = threadIdx.x - 32; // 0 .. NW*32-1
-    const bool ok = (*abort_flag == 0u);
-    for (uint32_t idx = ctid; idx < 8 * D; idx += NW * 32) {
-      const uint32_t g = idx / D;
-      const uint32_t d = idx % D;
-      float m_all = neg_infinity();
-#pragma unroll
-      for (uint32_t w = 0; w < NW; ++w) m_all = fmaxf(m_all, areas[w * L::WARP_AREA_FLOATS + 8 * D + g]);
-      float l_all = 0.f, o_all = 0.f;
-#pragma unroll
-      for (uint32_t w = 0; w < NW; ++w) {
-        const float mw = areas[w * L::WARP_AREA_FLOATS + 8 * D + g];
-        const float f = (mw == neg_infinity()) ? 0.f : fast_exp2(mw - m_all);
-        l_all += f * areas[w * L::WARP_AREA_FLOATS + 8 * D + 8 + g];
-        o_all += f * areas[w * L::WARP_AREA_FLOATS + g * D + d];
-      }
-      if constexpr (MODE == MODE_SPLIT) {
-        if (g < G && ok) {
-          const size_t head = static_cast<size_t>(seq) * args.num_heads + kv_head * G + g;
-          const size_t pidx = head * args.max_num_partitions + partition;
-          // normalised inside the partition (reference paged_attention_kernel_v2.hpp:386)
-          const float inv = (l_all > 0.f) ? (1.f / l_all) : 0.f;
-          args.tmp_out[pidx * D + d] = __float2half_rn(o_all * args.out_scale * inv);
-          if (d == 0) {
-            args.max_logits[pidx] = m_all * kLn2;
-            args.exp_sums[pidx] = l_all;
+          for (uint32_t w = 0; w < NW; ++w) {
+            const float mw = warp_m[w * 8 + g];
+            l_all += (mw == neg_infinity()) ? 0.f : fast_exp2(mw - m_all) * warp_l[w * 8 + g];
+          }
+          float4 lo = *reinterpret_cast<float4 *>(&o_acc[g * D + d0]);
+          float4 hi = *reinterpret_cast<float4 *>(&o_acc[g * D + d0 + 4]);
+          const float4 lo1 = *reinterpret_cast<float4 *>(&o_acc[8 * D + g * D + d0]);
+          const float4 hi1 = *reinterpret_cast<float4 *>(&o_acc[8 * D + g * D + d0 + 4]);
+          lo.x += lo1.x; lo.y += lo1.y; lo.z += lo1.z; lo.w += lo1.w;
+          hi.x += hi1.x; hi.y += hi1.y; hi.z += hi1.z; hi.w += hi1.w;
+          if constexpr (MODE == MODE_SPLIT) {
+            if (g < G && ok) {
+              const size_t head = static_cast<size_t>(cur.seq) * args.num_heads + cur.kv_head * G + g;
+              const size_t pidx = head * args.max_num_partitions + cur.partition;
+              // normalised inside the partition (reference paged_attention_kernel_v2.hpp:386)
+              const float inv = (l_all > 0.f) ? (args.out_scale / l_all) : 0.f;
+              uint4 packed;
+              packed.x = pack_half2(lo.x * inv, lo.y * inv);
+              packed.y = pack_half2(lo.z * inv, lo.w * inv);
+              packed.z = pack_half2(hi.x * inv, hi.y * inv);
+              packed.w = pack_half2(hi.z * inv, hi.w * inv);
+              *reinterpret_cast<uint4 *>(args.tmp_out + pidx * D + d0) = packed;
+              if (d0 == 0) {
+                args.max_logits[pidx] = m_all * kLn2;
+                args.exp_sums[pidx] = l_all;
+              }
+            }
+          } else {
+            // buffer 0 takes the CTA's unnormalised sum for the cluster merge
+            *reinterpret_cast<float4 *>(&o_acc[g * D + d0]) = lo;
+            *reinterpret_cast<float4 *>(&o_acc[g * D + d0 + 4]) = hi;
+            if (d0 == 0) {
+              cta_ml[g] = m_all;
+              cta_ml[8 + g] = l_all;
+            }
           }
         }
-      } else {
-        // unnormalised CTA result for the cluster merge
-        cta_area[g * D + d] = o_all;
-        if (d == 0) {
-          cta_area[8 * D + g] = m_all;
-          cta_area[8 * D + 8 + g] = l_all;
-        }
       }
+      cur = nxt;
     }
   }
 
@@ -496,37 +607,40 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     if (warp != 0) {
       const uint32_t G = args.group;
       const bool ok = (*abort_flag == 0u);
-      float *cta_area = reinterpret_cast<float *>(smem) + NW * L::WARP_AREA_FLOATS;
       const uint32_t ctid = threadIdx.x - 32;
       const uint32_t dims_per_rank = D / num_ranks; // cluster sizes are powers of two <= 8
-      for (uint32_t idx = ctid; idx < 8 * dims_per_rank; idx += NW * 32) {
+      for (uint32_t idx = ctid; idx < 8 * dims_per_rank; idx += NCONS) {
         const uint32_t g = idx / dims_per_rank;
         const uint32_t d = cta_rank * dims_per_rank + idx % dims_per_rank;
         float m_all = neg_infinity();
         for (uint32_t r = 0; r < num_ranks; ++r) {
-          const float *peer = cluster.map_shared_rank(cta_area, r);
-          m_all = fmaxf(m_all, peer[8 * D + g]);
+          const float *peer_ml = cluster.map_shared_rank(cta_ml, r);
+          m_all = fmaxf(m_all, peer_ml[g]);
         }
         float l_all = 0.f, o_all = 0.f;
         for (uint32_t r = 0; r < num_ranks; ++r) {
-          const float *peer = cluster.map_shared_rank(cta_area, r);
-          const float mr = peer[8 * D + g];
+          const float *peer_ml = cluster.map_shared_rank(cta_ml, r);
+          const float *peer_o = cluster.map_shared_rank(o_acc, r);
+          const float mr = peer_ml[g];
           const float f = (mr == neg_infinity()) ? 0.f : fast_exp2(mr - m_all);
-          l_all += f * peer[8 * D + 8 + g];
-          o_all += f * peer[g * D + d];
+          l_all += f * peer_ml[8 + g];
+          o_all += f * peer_o[g * D + d];
         }
         if (g < G && ok) {
           // acc * (1 / l) as the reference does (paged_attention_utils.hpp:834-835);
           // an empty context (l = 0) gives zeros
           const float inv = (l_all > 0.f) ? (1.f / l_all) : 0.f;
-          const size_t head = static_cast<size_t>(seq) * args.num_heads + kv_head * G + g;
+          const size_t head = static_cast<size_t>(first.seq) * args.num_heads + first.kv_head * G + g;
           args.out[head * D + d] = __float2half_rn(o_all * args.out_scale * inv);
         }
       }
     }
     cluster.sync(); // peers may still be reading this CTA's shared memory
   }
-  if (threadIdx.x == 32 && *abort_flag != 0u) atomicExch(&g_pa_device_status, 4);
+  if (*abort_flag != 0u) {
+    __nanosleep(200000); // give copies that are still in flight time to land
+    if (threadIdx.x == 32) atomicExch(&g_pa_device_status, 4);
+  }
 }
 
 // Second kernel of the split-context variant: one CTA per (sequence, head).

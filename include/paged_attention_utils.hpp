@@ -118,29 +118,41 @@ PA_DEV void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uin
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// ------------------------------------------------------------ FP8 -> fp16 pair
-// Each converter takes one 32-bit register holding four FP8 codes (bytes 0..3)
-// and returns the two selected codes as an fp16x2 register (first selected
-// byte in the low half).  Both formats convert exactly: every finite e5m2 and
-// e4m3 value is representable in fp16.
-template <int KV, int B_LO, int B_HI>
-PA_DEV uint32_t fp8_pair_to_half2(uint32_t v) {
+// ---------------------------------------------------------------- FP8 -> fp16
+// Both formats convert exactly: every finite e5m2 and e4m3 value is representable in fp16.
+// A register holds four FP8 codes (bytes 0..3); results are fp16x2 registers with the first
+// named byte in the low half.
+PA_DEV uint32_t e4m3x2_to_half2(uint16_t pair) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(pair));
+  return r;
+}
+
+// bytes (0,1) -> lo01, bytes (2,3) -> hi23   (K fragments: consecutive dims per lane)
+template <int KV>
+PA_DEV void fp8x4_to_half2x2(uint32_t v, uint32_t &lo01, uint32_t &hi23) {
   static_assert(KV == 1 || KV == 2, "FP8 formats only");
   if constexpr (KV == 1) {
-    // e5m2 is the high byte of an fp16: place each code in the high byte of a half
-    uint32_t r;
-    constexpr uint32_t sel = (B_HI << 12) | (4u << 8) | (B_LO << 4) | 4u;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(v), "r"(0u), "n"(sel));
-    return r;
+    // e5m2 is the high byte of an fp16: move each code into the high byte of a half
+    lo01 = __byte_perm(v, 0u, 0x1404);
+    hi23 = __byte_perm(v, 0u, 0x3424);
   } else {
-    uint32_t packed;
-    constexpr uint32_t sel = (4u << 12) | (4u << 8) | (B_HI << 4) | B_LO;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(packed) : "r"(v), "r"(0u), "n"(sel));
-    uint32_t r;
-    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo; }"
-        : "=r"(r)
-        : "r"(packed));
-    return r;
+    lo01 = e4m3x2_to_half2(static_cast<uint16_t>(v & 0xffffu));
+    hi23 = e4m3x2_to_half2(static_cast<uint16_t>(v >> 16));
+  }
+}
+
+// bytes (0,2) -> even, bytes (1,3) -> odd   (V fragments after a 16-bit transposing load)
+template <int KV>
+PA_DEV void fp8x4_to_even_odd_half2(uint32_t v, uint32_t &even, uint32_t &odd) {
+  static_assert(KV == 1 || KV == 2, "FP8 formats only");
+  if constexpr (KV == 1) {
+    even = __byte_perm(v, 0u, 0x2404);
+    odd = v & 0xff00ff00u; // bytes 1 and 3 already sit in the high byte of each half
+  } else {
+    const uint32_t t = __byte_perm(v, 0u, 0x3120); // [b0, b2, b1, b3]
+    even = e4m3x2_to_half2(static_cast<uint16_t>(t & 0xffffu));
+    odd = e4m3x2_to_half2(static_cast<uint16_t>(t >> 16));
   }
 }
 
