@@ -277,6 +277,8 @@ def main() -> None:
                     help="override the entry point the configuration names")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kv", default=None, choices=["float16", "float8_e5m2", "float8_e4m3fn"],
+                    help="override the KV cache type of the configuration")
     ap.add_argument("--num-seqs", type=int, default=None,
                     help="override the number of sequences (small cases for profiler captures)")
     a = ap.parse_args()
@@ -288,6 +290,8 @@ def main() -> None:
     spec = config_spec(a.config)
     if a.num_seqs is not None:
         spec["num_seqs"] = a.num_seqs
+    if a.kv is not None:
+        spec["kv"] = a.kv
     variant = a.variant or pick_variant(spec)
 
     if a.impl == "reference":

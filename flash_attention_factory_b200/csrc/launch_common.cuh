@@ -118,8 +118,8 @@ int get_device_info(DeviceInfo *info); // cached per device; defined in c_api.cu
 
 // Cluster size of the loop variant: enough CTAs to give every SM two, using
 // only what the host knows (num_seqs, num_kv_heads and the context-length hint).
-inline uint32_t choose_cluster_size(const pa_params *p, int sm_count, uint32_t tokens_per_stage) {
-  const uint64_t units = static_cast<uint64_t>(p->num_seqs) * p->num_kv_heads;
+inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_count, uint32_t tokens_per_stage) {
+  const uint64_t units = static_cast<uint64_t>(p->num_seqs) * (p->num_kv_heads / hpc);
   const uint64_t want = 2ull * static_cast<uint64_t>(sm_count);
   uint32_t cs = 1;
   while (cs < 8 && units * cs < want) cs *= 2;
@@ -150,8 +150,11 @@ AttnArgs make_attn_args(const pa_params *p) {
   a.max_blocks_per_seq = p->max_blocks_per_seq;
   a.max_num_partitions = p->max_num_partitions;
   a.block_shift = log2_pow2(p->block_size);
-  a.rows_per_box = p->block_size < policy::tokens_per_stage ? p->block_size : policy::tokens_per_stage;
-  a.boxes_per_stage = policy::tokens_per_stage / a.rows_per_box;
+  // KV heads per CTA: with 4 a warp owns a head and nothing is merged across warps
+  a.hpc = (p->num_kv_heads % 4 == 0) ? 4u : ((p->num_kv_heads % 2 == 0) ? 2u : 1u);
+  a.tokens_per_stage = policy::tokens_per_stage / a.hpc;
+  a.rows_per_box = p->block_size < a.tokens_per_stage ? p->block_size : a.tokens_per_stage;
+  a.boxes_per_stage = a.hpc * (a.tokens_per_stage / a.rows_per_box);
   const float kv_scale = (KV == KV_F16) ? 1.f : p->fp8_scale;
   // the FP8 scale is applied once, hoisted out of the dot products
   // (reference paged_attention_kernel_fp8_loop.hpp:333,545)
@@ -191,13 +194,13 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
   if (MODE == MODE_SPLIT) {
     // persistent CTAs, two per SM, each walking the (seq, partition, kv head) items with
     // stride gridDim.x; the TMA ring keeps streaming across item boundaries
-    const uint64_t items = static_cast<uint64_t>(p->num_kv_heads) * p->max_num_partitions * p->num_seqs;
+    const uint64_t items = static_cast<uint64_t>(p->num_kv_heads / args.hpc) * p->max_num_partitions * p->num_seqs;
     const uint64_t resident = 2ull * static_cast<uint64_t>(dev.sm_count);
     cfg.gridDim = dim3(static_cast<unsigned>(items < resident ? items : resident), 1, 1);
     cfg.numAttrs = 0;
   } else {
-    const uint32_t cs = choose_cluster_size(p, dev.sm_count, policy::tokens_per_stage);
-    cfg.gridDim = dim3(cs, p->num_kv_heads, p->num_seqs);
+    const uint32_t cs = choose_cluster_size(p, args.hpc, dev.sm_count, args.tokens_per_stage);
+    cfg.gridDim = dim3(cs, p->num_kv_heads / args.hpc, p->num_seqs);
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = cs;
     attr[0].val.clusterDim.y = 1;

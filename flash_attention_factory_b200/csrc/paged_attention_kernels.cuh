@@ -1,12 +1,12 @@
 // Device kernels of the B200 paged-attention decode library (sm_100a).
 //
 // One templated attention kernel serves the four entry points:
-//   MODE_LOOP   one (sequence, KV head) per thread-block cluster, the context
+//   MODE_LOOP   one (sequence, KV-head group) per thread-block cluster, the context
 //               split over the cluster's CTAs and merged through distributed
 //               shared memory; writes `out`
 //               (reference paged_attention_loop_kernel, paged_attention_kernel_loop.hpp:42-637)
-//   MODE_SPLIT  one (sequence, KV head, partition) per CTA; writes max_logits,
-//               exp_sums and the fp16 partial output
+//   MODE_SPLIT  persistent CTAs walking (sequence, partition, KV-head group) items;
+//               writes max_logits, exp_sums and the fp16 partial output
 //               (reference paged_attention_kernel, paged_attention_kernel_v2.hpp:42-588)
 // with the KV cache stored as fp16, e5m2 or e4m3 (FP8 dequantised in
 // registers, reference paged_attention_kernel_fp8_loop.hpp:270-278,328-333,540-545).
@@ -14,16 +14,20 @@
 // (reference paged_attention_reduce, paged_attention_kernel_v2.hpp:594-970).
 //
 // Structure of the attention kernel: warp 0 walks the block table and issues
-// tiled TMA copies (one box per KV block and 128-byte slab) into a ring of
-// shared-memory stages guarded by full/empty mbarriers; warps 1..4 each own 16
-// tokens of every stage.  The GQA query group sits on the N=8 extent of
-// mma.m16n8k16 and the tokens on M, so a KV byte is read from HBM once for the
-// whole group:
+// tiled TMA copies (one box per KV block, KV head and 128-byte slab) into a
+// ring of shared-memory stages guarded by full/empty mbarriers; warps 1..4
+// each own 16 rows of every stage.  A CTA works on `hpc` (1, 2 or 4)
+// neighbouring KV heads at once: with hpc = 4 a warp owns one KV head and sees
+// every token of the item, so nothing has to be merged across warps; with
+// fewer heads the warps split the tokens and merge through shared memory in a
+// fixed order.  The GQA query group sits on the N=8 extent of mma.m16n8k16 and
+// the tokens on M, so a KV byte is read from HBM once for the whole group:
 //   S^T[tok, g] = K[tok, d] . Q^T[d, g]          (A = K via ldmatrix)
 //   O^T[d, g]  += V^T[d, tok] . P^T[tok, g]      (A = V via ldmatrix.trans)
 // Softmax is online per warp in the log2 domain with warp-shuffle column
-// maxima; the four warps' (max, sum, acc) are merged through shared memory at
-// the end.  Every wait on an mbarrier is bounded (pa::mbar_wait_bounded).
+// maxima; the accumulator is rescaled only when the running maximum has grown
+// by more than kRescaleThreshold.  Every wait on an mbarrier is bounded
+// (pa::mbar_wait_bounded).
 #pragma once
 
 #include <cooperative_groups.h>
@@ -57,39 +61,48 @@ struct AttnArgs {
   uint32_t group;
   uint32_t max_blocks_per_seq;
   uint32_t max_num_partitions;
-  uint32_t block_shift;     // log2(block_size)
-  uint32_t rows_per_box;    // min(block_size, tokens_per_stage)
-  uint32_t boxes_per_stage; // tokens_per_stage / rows_per_box
-  float scale_log2;         // sm_scale * fp8_scale * log2(e), > 0
-  float out_scale;          // fp8_scale (1 for fp16)
+  uint32_t block_shift;      // log2(block_size)
+  uint32_t hpc;              // KV heads per CTA: 1, 2 or 4 (divides num_kv_heads)
+  uint32_t tokens_per_stage; // 64 / hpc
+  uint32_t rows_per_box;     // min(block_size, tokens_per_stage)
+  uint32_t boxes_per_stage;  // hpc * tokens_per_stage / rows_per_box: 1, 2 or 4
+  float scale_log2;          // sm_scale * fp8_scale * log2(e), > 0
+  float out_scale;           // fp8_scale (1 for fp16)
 };
 
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kLog2e = 1.4426950408889634f;
+// The exponent reference of the online softmax follows the running maximum only in
+// steps larger than this (log2 units), so weights stay below 2^8 and most tiles skip
+// the rescaling of the accumulator.
+constexpr float kRescaleThreshold = 8.0f;
 
 template <int D, int KV>
 struct SmemLayout {
   using policy = paged_attention_policy_v2<D, KV>;
   using geo = typename policy::geometry;
   static constexpr uint32_t NW = policy::consumer_warps;
-  static constexpr uint32_t TS = policy::tokens_per_stage;
+  static constexpr uint32_t ROWS = policy::tokens_per_stage; // 64 rows: hpc heads x 64/hpc tokens
   static constexpr uint32_t NSTAGES = policy::ring_stages;
-  static constexpr uint32_t SLAB_TILE = TS * geo::slab_bytes;     // one slab of one stage
+  static constexpr uint32_t SLAB_TILE = ROWS * geo::slab_bytes;   // one slab of one stage
   static constexpr uint32_t KV_TILE = geo::num_slabs * SLAB_TILE; // K (or V) of one stage
   static constexpr uint32_t STAGE_BYTES = 2 * KV_TILE;
   static constexpr uint32_t RING_BYTES = NSTAGES * STAGE_BYTES;
-  // merge scratch after the ring: two O[8][D] buffers that the consumer warps fill in a
-  // fixed order (warps 0,1 store, warps 2,3 add: the result does not depend on timing),
-  // per-warp (max, sum) of the 8 query columns, and the CTA's merged (max, sum)
-  static_assert(NW == 4, "the two-round merge below is written for four consumer warps");
-  static constexpr uint32_t OACC_OFFSET = RING_BYTES;
-  static constexpr uint32_t OACC_BYTES = 2 * 8 * D * 4;
-  static constexpr uint32_t WARP_ML_OFFSET = OACC_OFFSET + OACC_BYTES; // m[NW][8], l[NW][8]
-  static constexpr uint32_t WARP_ML_BYTES = 2 * 2 * NW * 8 * 4; // double-buffered by item parity
-  static constexpr uint32_t CTA_ML_OFFSET = WARP_ML_OFFSET + WARP_ML_BYTES; // M[8], L[8]
-  static constexpr uint32_t BAR_OFFSET = CTA_ML_OFFSET + 64;
+  static_assert(NW == 4, "warp <-> (head, token slice) mapping is written for four consumer warps");
+  // split mode, fewer than 4 heads per CTA: two O[8][D] buffers filled in a fixed order
+  static constexpr uint32_t MERGE_OFFSET = RING_BYTES;
+  static constexpr uint32_t MERGE_BYTES = 2 * 8 * D * 4;
+  // per-warp (reference max, true max, sum) of the 8 query columns, double-buffered by item parity
+  static constexpr uint32_t WARP_STATS_OFFSET = MERGE_OFFSET + MERGE_BYTES;
+  static constexpr uint32_t WARP_STATS_FLOATS = 3 * NW * 8;
+  static constexpr uint32_t WARP_STATS_BYTES = 2 * WARP_STATS_FLOATS * 4;
+  static constexpr uint32_t BAR_OFFSET = WARP_STATS_OFFSET + WARP_STATS_BYTES;
   static constexpr uint32_t TOTAL_BYTES = BAR_OFFSET + 2 * NSTAGES * 8 + 16;
   static constexpr uint32_t DYN_SMEM = TOTAL_BYTES + 1024; // slack for 1024-byte alignment
+  // loop mode: every warp parks (O[8][D], m[8], l[8]) on the (by then idle) ring for the
+  // cluster-wide merge
+  static constexpr uint32_t WARP_AREA_FLOATS = 8 * D + 16;
+  static_assert(NW * WARP_AREA_FLOATS * 4 <= RING_BYTES, "cluster merge scratch must fit in the ring");
 };
 
 // d index of accumulator tile `tile`, row half `h` (0: rows gid, 1: rows gid+8)
@@ -103,34 +116,35 @@ __device__ __forceinline__ uint32_t acc_dim_index(uint32_t tile, uint32_t h, uin
   }
 }
 
-// One unit of work of a CTA: tokens [tok_begin, tok_end) of (seq, kv_head).
+// One unit of work of a CTA: tokens [tok_begin, tok_end) of KV heads
+// [head_base, head_base + hpc) of one sequence.
 struct WorkItem {
-  uint32_t linear; // position in the dense (seq, partition, kv_head) enumeration (split mode)
-  uint32_t seq, kv_head, partition;
+  uint32_t linear; // position in the dense (seq, partition, head group) enumeration (split mode)
+  uint32_t seq, head_base, partition;
   uint32_t tok_begin, tok_end;
   bool valid;
 };
 
 // Split mode: CTA b handles the items b, b + gridDim.x, ... of the dense enumeration with
-// the KV head fastest (CTAs that run together stream neighbouring rows of the same KV
+// the head group fastest (CTAs that run together stream neighbouring rows of the same KV
 // blocks); partitions that start at or past the context are skipped and their scratch rows
 // stay untouched (reference paged_attention_kernel_v2.hpp:194-200,577-579).
 template <uint32_t PARTITION>
 __device__ __forceinline__ WorkItem find_split_item(uint32_t linear, const AttnArgs &args) {
   WorkItem it{};
-  const uint32_t hk = args.num_kv_heads;
-  const uint32_t per_seq = hk * args.max_num_partitions;
+  const uint32_t groups = args.num_kv_heads / args.hpc;
+  const uint32_t per_seq = groups * args.max_num_partitions;
   const uint32_t total = per_seq * args.num_seqs;
   it.valid = false;
   while (linear < total) {
     const uint32_t seq = linear / per_seq;
     const uint32_t rem = linear - seq * per_seq;
-    const uint32_t part = rem / hk;
+    const uint32_t part = rem / groups;
     const uint32_t ctx = __ldg(args.context_lens + seq);
     if (part * PARTITION < ctx) {
       it.linear = linear;
       it.seq = seq;
-      it.kv_head = rem - part * hk;
+      it.head_base = (rem - part * groups) * args.hpc;
       it.partition = part;
       it.tok_begin = part * PARTITION;
       it.tok_end = min(ctx, it.tok_begin + PARTITION);
@@ -144,11 +158,11 @@ __device__ __forceinline__ WorkItem find_split_item(uint32_t linear, const AttnA
 
 template <int D, int KV>
 __device__ __forceinline__ void load_q_fragments(uint32_t (&qf)[D / 16][2], const AttnArgs &args,
-                                                 const WorkItem &it, uint32_t gid, uint32_t t4) {
+                                                 uint32_t seq, uint32_t kv_head, uint32_t gid,
+                                                 uint32_t t4) {
   // B operand of S^T = K . Q^T: column n = gid is the query head inside the group
   const uint32_t G = args.group;
-  const __half *qrow =
-      args.query + (static_cast<size_t>(it.seq) * args.num_heads + it.kv_head * G + gid) * D;
+  const __half *qrow = args.query + (static_cast<size_t>(seq) * args.num_heads + kv_head * G + gid) * D;
 #pragma unroll
   for (uint32_t ks = 0; ks < D / 16; ++ks) {
     if (gid < G) {
@@ -177,7 +191,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   using policy = typename L::policy;
   using geo = typename L::geo;
   constexpr uint32_t NW = L::NW;
-  constexpr uint32_t TS = L::TS;
   constexpr uint32_t NSTAGES = L::NSTAGES;
   constexpr uint32_t KSTEPS = D / 16; // MMA k-steps of QK^T == accumulator tiles of PV
   constexpr uint32_t NCONS = NW * 32; // consumer threads
@@ -187,9 +200,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   // The offset is identical in every CTA, so cluster-mapped addresses line up.
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t *smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  float *o_acc = reinterpret_cast<float *>(smem + L::OACC_OFFSET);
-  float *warp_ml = reinterpret_cast<float *>(smem + L::WARP_ML_OFFSET); // [2][m|l][NW][8]
-  float *cta_ml = reinterpret_cast<float *>(smem + L::CTA_ML_OFFSET);  // M[8], L[8]
+  float *merge_buf = reinterpret_cast<float *>(smem + L::MERGE_OFFSET);
+  float *warp_stats = reinterpret_cast<float *>(smem + L::WARP_STATS_OFFSET);
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + L::BAR_OFFSET);
   uint64_t *empty_bar = full_bar + NSTAGES;
   volatile uint32_t *abort_flag =
@@ -197,6 +209,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t hpc = args.hpc;
+  const uint32_t tps = args.tokens_per_stage;
 
   // ---- the first work item of this CTA (integer bookkeeping, bit-exact)
   uint32_t cta_rank = 0, num_ranks = 1;
@@ -209,14 +223,14 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     cta_rank = cluster.block_rank();
     num_ranks = cluster.num_blocks();
     first.seq = blockIdx.z;
-    first.kv_head = blockIdx.y;
+    first.head_base = blockIdx.y * hpc;
     first.partition = 0;
     const uint32_t ctx = args.context_lens[first.seq];
     // the context is cut into whole stages, spread evenly over the CTAs of the cluster
-    const uint32_t total_stages = divide_round_up(ctx, TS);
+    const uint32_t total_stages = divide_round_up(ctx, tps);
     const uint32_t stages_per_rank = divide_round_up(total_stages, num_ranks);
-    first.tok_begin = min(ctx, cta_rank * stages_per_rank * TS);
-    first.tok_end = min(ctx, (cta_rank + 1) * stages_per_rank * TS);
+    first.tok_begin = min(ctx, cta_rank * stages_per_rank * tps);
+    first.tok_end = min(ctx, (cta_rank + 1) * stages_per_rank * tps);
     first.valid = true;
   }
 
@@ -238,51 +252,58 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
     const uint32_t rows = args.rows_per_box;
     const uint32_t bps = args.boxes_per_stage;
+    const uint32_t chunks_per_stage = bps / hpc;      // token chunks (boxes per head) in a stage
     const uint32_t box_bytes = rows * geo::row_bytes; // K (or V) bytes of one box
     const uint32_t ring_base = smem_u32(smem);
     const uint32_t row_mask = (1u << args.block_shift) - 1u;
+    // lane -> (token chunk of the batch, head inside the CTA's head group), head fastest
+    const uint32_t lane_chunk = lane / hpc;
+    const uint32_t lane_head = lane % hpc;
+    const uint32_t chunks_per_batch = 32 / hpc;
     uint32_t slot = 0, phase = 0; // ring position, continuous across work items
     bool alive = true;
 
-    auto fetch_block_id = [&](const WorkItem &it, uint32_t box) -> uint32_t {
-      const uint32_t tok = it.tok_begin + box * rows;
+    auto fetch_block_id = [&](const WorkItem &it, uint32_t chunk) -> uint32_t {
+      const uint32_t tok = it.tok_begin + chunk * rows;
       if (!it.valid || tok >= it.tok_end) return 0u;
       return __ldg(args.block_tables + static_cast<size_t>(it.seq) * args.max_blocks_per_seq +
                    (tok >> args.block_shift));
     };
 
     WorkItem cur = first;
-    uint32_t block_id_next = fetch_block_id(cur, lane);
+    uint32_t block_id_next = fetch_block_id(cur, lane_chunk);
     while (cur.valid && alive) {
       WorkItem nxt{};
       nxt.valid = false;
       if constexpr (MODE == MODE_SPLIT)
         nxt = find_split_item<policy::partition_size>(cur.linear + gridDim.x, args);
-      const uint32_t total_boxes = divide_round_up(cur.tok_end - cur.tok_begin, rows);
-      const int32_t x0 = static_cast<int32_t>(cur.kv_head * D);
-      for (uint32_t batch0 = 0; batch0 < total_boxes && alive; batch0 += 32) {
-        const uint32_t box = batch0 + lane;
+      const uint32_t total_chunks = divide_round_up(cur.tok_end - cur.tok_begin, rows);
+      const int32_t x0 = static_cast<int32_t>((cur.head_base + lane_head) * D);
+      for (uint32_t chunk0 = 0; chunk0 < total_chunks && alive; chunk0 += chunks_per_batch) {
+        const uint32_t chunk = chunk0 + lane_chunk;
         const uint32_t block_id = block_id_next;
         // prefetch the table entries of the next batch (of this item or of the next one)
-        block_id_next = (batch0 + 32 < total_boxes) ? fetch_block_id(cur, box + 32)
-                                                    : fetch_block_id(nxt, lane);
-        const bool valid = box < total_boxes;
-        const uint32_t tok = cur.tok_begin + box * rows;
+        block_id_next = (chunk0 + chunks_per_batch < total_chunks)
+                            ? fetch_block_id(cur, chunk + chunks_per_batch)
+                            : fetch_block_id(nxt, lane_chunk);
+        const bool valid = chunk < total_chunks;
+        const uint32_t tok = cur.tok_begin + chunk * rows;
         const int32_t y = static_cast<int32_t>((block_id << args.block_shift) + (tok & row_mask));
-        const uint32_t boxes_in_batch = min(32u, total_boxes - batch0);
-        const uint32_t stages_in_batch = divide_round_up(boxes_in_batch, bps);
+        const uint32_t chunks_in_batch = min(chunks_per_batch, total_chunks - chunk0);
+        const uint32_t stages_in_batch = divide_round_up(chunks_in_batch, chunks_per_stage);
         for (uint32_t sb = 0; sb < stages_in_batch; ++sb) {
           if (lane == 0) {
             alive = mbar_wait_bounded(&empty_bar[slot], phase ^ 1u, abort_flag);
             if (alive) {
-              const uint32_t boxes_here = min(bps, boxes_in_batch - sb * bps);
-              mbar_arrive_expect_tx(&full_bar[slot], boxes_here * box_bytes * 2u);
+              const uint32_t chunks_here = min(chunks_per_stage, chunks_in_batch - sb * chunks_per_stage);
+              mbar_arrive_expect_tx(&full_bar[slot], chunks_here * hpc * box_bytes * 2u);
             }
           }
           alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
           if (!alive) break;
-          if (valid && lane / bps == sb) {
-            const uint32_t row0 = (lane % bps) * rows;
+          if (valid && lane_chunk / chunks_per_stage == sb) {
+            // rows of a stage: head-major, tokens_per_stage rows per head
+            const uint32_t row0 = lane_head * tps + (lane_chunk % chunks_per_stage) * rows;
             const uint32_t stage_base = ring_base + slot * L::STAGE_BYTES;
 #pragma unroll
             for (uint32_t sl = 0; sl < geo::num_slabs; ++sl) {
@@ -302,12 +323,16 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
   } else {
     // =========================== consumer warps ==========================
-    const uint32_t cw = warp - 1; // 0..NW-1
+    const uint32_t cw = warp - 1; // 0..NW-1: rows [16 cw, 16 cw + 16) of every stage
     const uint32_t gid = lane >> 2;
     const uint32_t t4 = lane & 3u;
     const uint32_t G = args.group;
     const uint32_t ctid = threadIdx.x - 32; // 0 .. NCONS-1
     const float scale = args.scale_log2;
+    // warp -> (head inside the group, 16-token slice inside the stage)
+    const uint32_t slices = NW / hpc; // token slices per head: 4, 2 or 1
+    const uint32_t my_head = cw / slices;
+    const uint32_t my_slice = cw % slices;
 
     // lane-dependent, stage-independent parts of the ldmatrix addresses; the chunk pair
     // 2k, 2k+1 of a slab is reached by XOR-ing (k << 5) into the address
@@ -322,46 +347,65 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     bool alive = true;
     uint32_t qf[KSTEPS][2];
     WorkItem cur = first;
-    if (cur.valid) load_q_fragments<D, KV>(qf, args, cur, gid, t4);
+    if (cur.valid) load_q_fragments<D, KV>(qf, args, cur.seq, cur.head_base + my_head, gid, t4);
+
+    // state of query columns g = 2*t4 and 2*t4+1, log2 domain: m_ref is the exponent
+    // reference the weights are taken against, m_true the running maximum
+    float m_ref[2], m_true[2], l_run[2];
+    float acc[KSTEPS][4];
 
     while (cur.valid) {
       WorkItem nxt{};
       nxt.valid = false;
       if constexpr (MODE == MODE_SPLIT)
         nxt = find_split_item<policy::partition_size>(cur.linear + gridDim.x, args);
+      const uint32_t kv_head = cur.head_base + my_head;
 
-      // running softmax state of columns g = 2*t4 and 2*t4+1, in the log2 domain
-      float m_run[2] = {neg_infinity(), neg_infinity()};
-      float l_run[2] = {0.f, 0.f}; // per-lane partial sums; reduced over gid at the end
-      float acc[KSTEPS][4];
+      m_ref[0] = m_ref[1] = m_true[0] = m_true[1] = neg_infinity();
+      l_run[0] = l_run[1] = 0.f; // per-lane partial sums; reduced over gid at the end
 #pragma unroll
       for (uint32_t i = 0; i < KSTEPS; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
       // The sink is one extra logit with a zero value vector, attached to the first tokens
       // of the context only (reference paged_attention_kernel_loop.hpp:387-401).
-      if (args.sinks != nullptr && cw == 0 && cur.tok_begin == 0) {
+      if (args.sinks != nullptr && my_slice == 0 && cur.tok_begin == 0) {
 #pragma unroll
         for (uint32_t j = 0; j < 2; ++j) {
           const uint32_t g = 2 * t4 + j;
           if (g < G) {
-            m_run[j] = __half2float(args.sinks[cur.kv_head * G + g]) * kLog2e;
+            m_ref[j] = m_true[j] = __half2float(args.sinks[kv_head * G + g]) * kLog2e;
             l_run[j] = (gid == 0) ? 1.f : 0.f;
           }
         }
       }
 
       const uint32_t my_tokens = cur.tok_end - cur.tok_begin;
-      const uint32_t my_stages = divide_round_up(my_tokens, TS);
+      const uint32_t my_stages = divide_round_up(my_tokens, tps);
       for (uint32_t st = 0; st < my_stages; ++st) {
         // after an abort the loops keep their shape (the named barriers below need every
         // consumer warp) but no longer wait or compute
         if (alive) alive = mbar_wait_bounded(&full_bar[slot], phase, abort_flag);
-        const uint32_t tile_tok0 = st * TS + cw * 16; // first token of this warp's slice
+        const uint32_t tile_tok0 = st * tps + my_slice * 16; // first token of this warp's tile
         if (alive && tile_tok0 < my_tokens) {
           const uint32_t n_valid = min(16u, my_tokens - tile_tok0);
-          const bool partial = n_valid < 16u;
           const uint32_t k_base = ring_base + slot * L::STAGE_BYTES;
           const uint32_t v_base = k_base + L::KV_TILE;
           const uint32_t k_addr = k_base + lm_off_a;
+          if (n_valid < 16u) {
+            // Last tile of the context: clear the V rows past it (unused tail of the last
+            // block, or rows no copy of this stage wrote), so that 0 * garbage stays 0.
+            const uint32_t zero_rows = 16u - n_valid;
+            constexpr uint32_t CPR = geo::slab_bytes / 16; // 16-byte chunks per row
+            for (uint32_t sl = 0; sl < geo::num_slabs; ++sl) {
+              for (uint32_t c = lane; c < zero_rows * CPR; c += 32) {
+                const uint32_t row = cw * 16 + n_valid + c / CPR;
+                const uint32_t addr = v_base + sl * L::SLAB_TILE + row * geo::slab_bytes + (c % CPR) * 16;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+              }
+            }
+            // order these generic-proxy writes before the TMA (async proxy) refill of the slot
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+          }
 
           // ---- S^T = K . Q^T  (two accumulation chains shorten the dependency)
           float s_a[4] = {0.f, 0.f, 0.f, 0.f};
@@ -393,7 +437,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           float c[4];
 #pragma unroll
           for (uint32_t j = 0; j < 4; ++j) c[j] = s_a[j] + s_b[j];
-          if (partial) {
+          if (n_valid < 16u) {
             // tokens past the context never count, whatever the cache holds there
             // (reference paged_attention_kernel_loop.hpp:323-327)
             if (gid >= n_valid) c[0] = c[1] = neg_infinity();
@@ -401,16 +445,13 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           }
           // ---- online softmax (reference paged_attention_kernel_loop.hpp:382-419);
           // scale > 0, so the maximum commutes with the scaling
-          const float m_new0 = fmaxf(m_run[0], quad_column_max(fmaxf(c[0], c[2])) * scale);
-          const float m_new1 = fmaxf(m_run[1], quad_column_max(fmaxf(c[1], c[3])) * scale);
-          const float p0 = fast_exp2(fmaf(c[0], scale, -m_new0));
-          const float p1 = fast_exp2(fmaf(c[1], scale, -m_new1));
-          const float p2 = fast_exp2(fmaf(c[2], scale, -m_new0));
-          const float p3 = fast_exp2(fmaf(c[3], scale, -m_new1));
-          const bool grew = (m_new0 != m_run[0]) || (m_new1 != m_run[1]);
-          if (__any_sync(0xffffffffu, grew)) {
-            const float r0 = fast_exp2(m_run[0] - m_new0);
-            const float r1 = fast_exp2(m_run[1] - m_new1);
+          m_true[0] = fmaxf(m_true[0], quad_column_max(fmaxf(c[0], c[2])) * scale);
+          m_true[1] = fmaxf(m_true[1], quad_column_max(fmaxf(c[1], c[3])) * scale);
+          const bool stale = (m_true[0] > m_ref[0] + kRescaleThreshold) ||
+                             (m_true[1] > m_ref[1] + kRescaleThreshold);
+          if (__any_sync(0xffffffffu, stale)) {
+            const float r0 = (m_ref[0] == neg_infinity()) ? 0.f : fast_exp2(m_ref[0] - m_true[0]);
+            const float r1 = (m_ref[1] == neg_infinity()) ? 0.f : fast_exp2(m_ref[1] - m_true[1]);
             l_run[0] *= r0;
             l_run[1] *= r1;
 #pragma unroll
@@ -420,21 +461,19 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
               acc[i][2] *= r0;
               acc[i][3] *= r1;
             }
-            m_run[0] = m_new0;
-            m_run[1] = m_new1;
+            m_ref[0] = m_true[0];
+            m_ref[1] = m_true[1];
           }
+          const float p0 = fast_exp2(fmaf(c[0], scale, -m_ref[0]));
+          const float p1 = fast_exp2(fmaf(c[1], scale, -m_ref[1]));
+          const float p2 = fast_exp2(fmaf(c[2], scale, -m_ref[0]));
+          const float p3 = fast_exp2(fmaf(c[3], scale, -m_ref[1]));
           l_run[0] += p0 + p2; // fp32 sum of the unrounded weights
           l_run[1] += p1 + p3;
           // P rounded to fp16 for the MMA, transposed into the B-operand layout
           const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1)); // tokens 0..7
           const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3)); // tokens 8..15
 
-          // masks that clear V of tokens past the context, so that 0 * garbage stays 0
-          uint32_t mask_lo = 0xffffffffu, mask_hi = 0xffffffffu;
-          if (partial) {
-            mask_lo = ((2 * t4 < n_valid) ? 0x0000ffffu : 0u) | ((2 * t4 + 1 < n_valid) ? 0xffff0000u : 0u);
-            mask_hi = ((2 * t4 + 8 < n_valid) ? 0x0000ffffu : 0u) | ((2 * t4 + 9 < n_valid) ? 0xffff0000u : 0u);
-          }
           // ---- O^T += V^T . P^T
           if constexpr (KV == KV_F16) {
             const uint32_t v_addr = v_base + lm_off_b;
@@ -442,12 +481,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
             for (uint32_t i = 0; i < KSTEPS; ++i) {
               uint32_t a[4];
               ldmatrix_x4_trans(a, (v_addr ^ ((i % PAIRS_PER_SLAB) << 5)) + (i / PAIRS_PER_SLAB) * L::SLAB_TILE);
-              if (partial) {
-                a[0] &= mask_lo;
-                a[1] &= mask_lo;
-                a[2] &= mask_hi;
-                a[3] &= mask_hi;
-              }
               mma_m16n8k16(acc[i], a, pb0, pb1);
             }
           } else {
@@ -465,16 +498,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
               fp8x4_to_even_odd_half2<KV>(r[2], ae[1], ao[1]);
               fp8x4_to_even_odd_half2<KV>(r[1], ae[2], ao[2]);
               fp8x4_to_even_odd_half2<KV>(r[3], ae[3], ao[3]);
-              if (partial) {
-                ae[0] &= mask_lo;
-                ae[1] &= mask_lo;
-                ae[2] &= mask_hi;
-                ae[3] &= mask_hi;
-                ao[0] &= mask_lo;
-                ao[1] &= mask_lo;
-                ao[2] &= mask_hi;
-                ao[3] &= mask_hi;
-              }
               mma_m16n8k16(acc[2 * q], ae, pb0, pb1);
               mma_m16n8k16(acc[2 * q + 1], ao, pb0, pb1);
             }
@@ -489,88 +512,133 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
       }
 
-      // Q of the next item: issued now so that the loads fly during the merge below
-      if (nxt.valid) load_q_fragments<D, KV>(qf, args, nxt, gid, t4);
+      // Q of the next item: issued now so that the loads fly during the epilogue below
+      if (nxt.valid) load_q_fragments<D, KV>(qf, args, nxt.seq, nxt.head_base + my_head, gid, t4);
 
-      // ---- merge the consumer warps of this CTA through shared memory.  The (max, sum)
-      // slots alternate between items: a warp may publish the next item's values while a
-      // slower warp still reads this item's.
-      float *warp_m = warp_ml + item_parity * (2 * NW * 8);
-      float *warp_l = warp_m + NW * 8;
-      item_parity ^= 1u;
       l_run[0] = quad_column_sum(l_run[0]);
       l_run[1] = quad_column_sum(l_run[1]);
-      if (gid == 0) {
-        warp_m[cw * 8 + 2 * t4] = m_run[0];
-        warp_m[cw * 8 + 2 * t4 + 1] = m_run[1];
-        warp_l[cw * 8 + 2 * t4] = l_run[0];
-        warp_l[cw * 8 + 2 * t4 + 1] = l_run[1];
-      }
-      named_barrier_sync(1, NCONS);
-      {
-        float f[2];
+      const bool ok = (*abort_flag == 0u);
+
+      if constexpr (MODE == MODE_SPLIT) {
+        if (hpc == NW) {
+          // ---- one warp per KV head: the warp holds the whole partition, write it out
+          // (max_logits / exp_sums / tmp_out, reference paged_attention_kernel_v2.hpp:425-442,532-546)
+          const size_t head0 = static_cast<size_t>(cur.seq) * args.num_heads + kv_head * G;
 #pragma unroll
-        for (uint32_t j = 0; j < 2; ++j) {
-          float m_all = neg_infinity();
-#pragma unroll
-          for (uint32_t w = 0; w < NW; ++w) m_all = fmaxf(m_all, warp_m[w * 8 + 2 * t4 + j]);
-          f[j] = (m_run[j] == neg_infinity()) ? 0.f : fast_exp2(m_run[j] - m_all);
-        }
-        // round 1: warps 0 and 1 store their rescaled accumulators into buffers 0 and 1
-        float *buf = o_acc + (cw & 1u) * (8 * D);
-        if (cw < 2) {
-#pragma unroll
-          for (uint32_t i = 0; i < KSTEPS; ++i) {
-#pragma unroll
-            for (uint32_t h = 0; h < 2; ++h) {
-              const uint32_t d = acc_dim_index<KV>(i, h, gid);
-              buf[(2 * t4) * D + d] = acc[i][2 * h] * f[0];
-              buf[(2 * t4 + 1) * D + d] = acc[i][2 * h + 1] * f[1];
-            }
-          }
-        }
-        named_barrier_sync(1, NCONS);
-        // round 2: warps 2 and 3 add theirs (each element has exactly one writer)
-        if (cw >= 2) {
-#pragma unroll
-          for (uint32_t i = 0; i < KSTEPS; ++i) {
-#pragma unroll
-            for (uint32_t h = 0; h < 2; ++h) {
-              const uint32_t d = acc_dim_index<KV>(i, h, gid);
-              buf[(2 * t4) * D + d] += acc[i][2 * h] * f[0];
-              buf[(2 * t4 + 1) * D + d] += acc[i][2 * h + 1] * f[1];
-            }
-          }
-        }
-      }
-      named_barrier_sync(1, NCONS);
-      {
-        // thread -> (query column g, 8 consecutive dims)
-        constexpr uint32_t THREADS_PER_ROW = D / 8;
-        const uint32_t g = ctid / THREADS_PER_ROW;
-        const uint32_t d0 = (ctid % THREADS_PER_ROW) * 8;
-        const bool ok = (*abort_flag == 0u);
-        if (g < 8) {
-          float m_all = neg_infinity();
-#pragma unroll
-          for (uint32_t w = 0; w < NW; ++w) m_all = fmaxf(m_all, warp_m[w * 8 + g]);
-          float l_all = 0.f;
-#pragma unroll
-          for (uint32_t w = 0; w < NW; ++w) {
-            const float mw = warp_m[w * 8 + g];
-            l_all += (mw == neg_infinity()) ? 0.f : fast_exp2(mw - m_all) * warp_l[w * 8 + g];
-          }
-          float4 lo = *reinterpret_cast<float4 *>(&o_acc[g * D + d0]);
-          float4 hi = *reinterpret_cast<float4 *>(&o_acc[g * D + d0 + 4]);
-          const float4 lo1 = *reinterpret_cast<float4 *>(&o_acc[8 * D + g * D + d0]);
-          const float4 hi1 = *reinterpret_cast<float4 *>(&o_acc[8 * D + g * D + d0 + 4]);
-          lo.x += lo1.x; lo.y += lo1.y; lo.z += lo1.z; lo.w += lo1.w;
-          hi.x += hi1.x; hi.y += hi1.y; hi.z += hi1.z; hi.w += hi1.w;
-          if constexpr (MODE == MODE_SPLIT) {
+          for (uint32_t j = 0; j < 2; ++j) {
+            const uint32_t g = 2 * t4 + j;
             if (g < G && ok) {
-              const size_t head = static_cast<size_t>(cur.seq) * args.num_heads + cur.kv_head * G + g;
-              const size_t pidx = head * args.max_num_partitions + cur.partition;
+              const size_t pidx = (head0 + g) * args.max_num_partitions + cur.partition;
+              // report the true maximum; the sum is re-expressed relative to it
+              const float l_true = l_run[j] * fast_exp2(m_ref[j] - m_true[j]);
               // normalised inside the partition (reference paged_attention_kernel_v2.hpp:386)
+              const float inv = (l_run[j] > 0.f) ? (args.out_scale / l_run[j]) : 0.f;
+              __half *dst = args.tmp_out + pidx * D;
+              if constexpr (KV == KV_F16) {
+#pragma unroll
+                for (uint32_t i = 0; i < KSTEPS; ++i) {
+                  dst[i * 16 + gid] = __float2half_rn(acc[i][j] * inv);
+                  dst[i * 16 + 8 + gid] = __float2half_rn(acc[i][2 + j] * inv);
+                }
+              } else {
+#pragma unroll
+                for (uint32_t q = 0; q < KSTEPS / 2; ++q) {
+                  // even/odd tiles hold neighbouring dims: one 4-byte store per pair
+                  *reinterpret_cast<uint32_t *>(dst + q * 32 + 2 * gid) =
+                      pack_half2(acc[2 * q][j] * inv, acc[2 * q + 1][j] * inv);
+                  *reinterpret_cast<uint32_t *>(dst + q * 32 + 16 + 2 * gid) =
+                      pack_half2(acc[2 * q][2 + j] * inv, acc[2 * q + 1][2 + j] * inv);
+                }
+              }
+              if (gid == 0) {
+                args.max_logits[pidx] = m_true[j] * kLn2;
+                args.exp_sums[pidx] = l_true;
+              }
+            }
+          }
+        } else {
+          // ---- the warps of a head split the tokens: merge them through shared memory in
+          // a fixed order.  The stats slots alternate between items: a warp may publish the
+          // next item's values while a slower warp still reads this item's.
+          float *st_ref = warp_stats + item_parity * L::WARP_STATS_FLOATS;
+          float *st_true = st_ref + NW * 8;
+          float *st_sum = st_true + NW * 8;
+          item_parity ^= 1u;
+          if (gid == 0) {
+#pragma unroll
+            for (uint32_t j = 0; j < 2; ++j) {
+              st_ref[cw * 8 + 2 * t4 + j] = m_ref[j];
+              st_true[cw * 8 + 2 * t4 + j] = m_true[j];
+              st_sum[cw * 8 + 2 * t4 + j] = l_run[j];
+            }
+          }
+          named_barrier_sync(1, NCONS);
+          const uint32_t w0 = my_head * slices; // first warp of this warp's head
+          float f[2];
+#pragma unroll
+          for (uint32_t j = 0; j < 2; ++j) {
+            float m_all = neg_infinity();
+            for (uint32_t w = w0; w < w0 + slices; ++w) m_all = fmaxf(m_all, st_ref[w * 8 + 2 * t4 + j]);
+            f[j] = (m_ref[j] == neg_infinity()) ? 0.f : fast_exp2(m_ref[j] - m_all);
+          }
+          // hpc = 1: slices 0,1 store into buffers 0,1 and slices 2,3 add to them;
+          // hpc = 2: buffer = head, slice 0 stores and slice 1 adds
+          const uint32_t buf_id = (hpc == 1) ? (my_slice & 1u) : my_head;
+          const uint32_t round = (hpc == 1) ? (my_slice >> 1) : my_slice;
+          float *buf = merge_buf + buf_id * (8 * D);
+          if (round == 0) {
+#pragma unroll
+            for (uint32_t i = 0; i < KSTEPS; ++i) {
+#pragma unroll
+              for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t d = acc_dim_index<KV>(i, h, gid);
+                buf[(2 * t4) * D + d] = acc[i][2 * h] * f[0];
+                buf[(2 * t4 + 1) * D + d] = acc[i][2 * h + 1] * f[1];
+              }
+            }
+          }
+          named_barrier_sync(1, NCONS);
+          if (round == 1) {
+#pragma unroll
+            for (uint32_t i = 0; i < KSTEPS; ++i) {
+#pragma unroll
+              for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t d = acc_dim_index<KV>(i, h, gid);
+                buf[(2 * t4) * D + d] += acc[i][2 * h] * f[0];
+                buf[(2 * t4 + 1) * D + d] += acc[i][2 * h + 1] * f[1];
+              }
+            }
+          }
+          named_barrier_sync(1, NCONS);
+          // write out: thread -> (head, query column g, 8 consecutive dims)
+          constexpr uint32_t THREADS_PER_ROW = D / 8;
+          for (uint32_t idx = ctid; idx < hpc * 8 * THREADS_PER_ROW; idx += NCONS) {
+            const uint32_t hh = idx / (8 * THREADS_PER_ROW);
+            const uint32_t g = (idx / THREADS_PER_ROW) % 8;
+            const uint32_t d0 = (idx % THREADS_PER_ROW) * 8;
+            const uint32_t wb = hh * slices;
+            float mr_all = neg_infinity(), mt_all = neg_infinity();
+            for (uint32_t w = wb; w < wb + slices; ++w) {
+              mr_all = fmaxf(mr_all, st_ref[w * 8 + g]);
+              mt_all = fmaxf(mt_all, st_true[w * 8 + g]);
+            }
+            float l_all = 0.f;
+            for (uint32_t w = wb; w < wb + slices; ++w) {
+              const float mw = st_ref[w * 8 + g];
+              l_all += (mw == neg_infinity()) ? 0.f : fast_exp2(mw - mr_all) * st_sum[w * 8 + g];
+            }
+            const float *b0 = merge_buf + ((hpc == 1) ? 0u : hh) * (8 * D) + g * D + d0;
+            float4 lo = *reinterpret_cast<const float4 *>(b0);
+            float4 hi = *reinterpret_cast<const float4 *>(b0 + 4);
+            if (hpc == 1) {
+              const float4 lo1 = *reinterpret_cast<const float4 *>(b0 + 8 * D);
+              const float4 hi1 = *reinterpret_cast<const float4 *>(b0 + 8 * D + 4);
+              lo.x += lo1.x; lo.y += lo1.y; lo.z += lo1.z; lo.w += lo1.w;
+              hi.x += hi1.x; hi.y += hi1.y; hi.z += hi1.z; hi.w += hi1.w;
+            }
+            if (g < G && ok) {
+              const size_t head = static_cast<size_t>(cur.seq) * args.num_heads + (cur.head_base + hh) * G + g;
+              const size_t pidx = head * args.max_num_partitions + cur.partition;
               const float inv = (l_all > 0.f) ? (args.out_scale / l_all) : 0.f;
               uint4 packed;
               packed.x = pack_half2(lo.x * inv, lo.y * inv);
@@ -579,18 +647,30 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
               packed.w = pack_half2(hi.z * inv, hi.w * inv);
               *reinterpret_cast<uint4 *>(args.tmp_out + pidx * D + d0) = packed;
               if (d0 == 0) {
-                args.max_logits[pidx] = m_all * kLn2;
-                args.exp_sums[pidx] = l_all;
+                args.max_logits[pidx] = mt_all * kLn2;
+                args.exp_sums[pidx] = l_all * fast_exp2(mr_all - mt_all);
               }
             }
-          } else {
-            // buffer 0 takes the CTA's unnormalised sum for the cluster merge
-            *reinterpret_cast<float4 *>(&o_acc[g * D + d0]) = lo;
-            *reinterpret_cast<float4 *>(&o_acc[g * D + d0 + 4]) = hi;
-            if (d0 == 0) {
-              cta_ml[g] = m_all;
-              cta_ml[8 + g] = l_all;
-            }
+          }
+        }
+      } else {
+        // ---- loop mode: park (O, m_ref, l) of this warp on the idle ring for the cluster merge
+        named_barrier_sync(1, NCONS); // every consumer warp has finished reading the ring
+        float *area = reinterpret_cast<float *>(smem) + cw * L::WARP_AREA_FLOATS;
+        if (gid == 0) {
+#pragma unroll
+          for (uint32_t j = 0; j < 2; ++j) {
+            area[8 * D + 2 * t4 + j] = m_ref[j];
+            area[8 * D + 8 + 2 * t4 + j] = l_run[j];
+          }
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < KSTEPS; ++i) {
+#pragma unroll
+          for (uint32_t h = 0; h < 2; ++h) {
+            const uint32_t d = acc_dim_index<KV>(i, h, gid);
+            area[(2 * t4) * D + d] = acc[i][2 * h];
+            area[(2 * t4 + 1) * D + d] = acc[i][2 * h + 1];
           }
         }
       }
@@ -599,8 +679,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   }
 
   if constexpr (MODE == MODE_LOOP) {
-    // ---- merge the CTAs of the cluster through distributed shared memory;
-    // every thread of every CTA reaches both cluster barriers, also after an abort
+    // ---- merge over the warps that share a head and over the CTAs of the cluster, through
+    // distributed shared memory, in a fixed order.  Every thread of every CTA reaches both
+    // cluster barriers, also after an abort.
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
@@ -608,29 +689,35 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       const uint32_t G = args.group;
       const bool ok = (*abort_flag == 0u);
       const uint32_t ctid = threadIdx.x - 32;
+      const uint32_t slices = NW / hpc;
       const uint32_t dims_per_rank = D / num_ranks; // cluster sizes are powers of two <= 8
-      for (uint32_t idx = ctid; idx < 8 * dims_per_rank; idx += NCONS) {
-        const uint32_t g = idx / dims_per_rank;
+      float *areas = reinterpret_cast<float *>(smem);
+      for (uint32_t idx = ctid; idx < hpc * 8 * dims_per_rank; idx += NCONS) {
+        const uint32_t hh = idx / (8 * dims_per_rank);
+        const uint32_t g = (idx / dims_per_rank) % 8;
         const uint32_t d = cta_rank * dims_per_rank + idx % dims_per_rank;
         float m_all = neg_infinity();
         for (uint32_t r = 0; r < num_ranks; ++r) {
-          const float *peer_ml = cluster.map_shared_rank(cta_ml, r);
-          m_all = fmaxf(m_all, peer_ml[g]);
+          const float *peer = cluster.map_shared_rank(areas, r);
+          for (uint32_t w = hh * slices; w < (hh + 1) * slices; ++w)
+            m_all = fmaxf(m_all, peer[w * L::WARP_AREA_FLOATS + 8 * D + g]);
         }
         float l_all = 0.f, o_all = 0.f;
         for (uint32_t r = 0; r < num_ranks; ++r) {
-          const float *peer_ml = cluster.map_shared_rank(cta_ml, r);
-          const float *peer_o = cluster.map_shared_rank(o_acc, r);
-          const float mr = peer_ml[g];
-          const float f = (mr == neg_infinity()) ? 0.f : fast_exp2(mr - m_all);
-          l_all += f * peer_ml[8 + g];
-          o_all += f * peer_o[g * D + d];
+          const float *peer = cluster.map_shared_rank(areas, r);
+          for (uint32_t w = hh * slices; w < (hh + 1) * slices; ++w) {
+            const float *pa = peer + w * L::WARP_AREA_FLOATS;
+            const float mr = pa[8 * D + g];
+            const float f = (mr == neg_infinity()) ? 0.f : fast_exp2(mr - m_all);
+            l_all += f * pa[8 * D + 8 + g];
+            o_all += f * pa[g * D + d];
+          }
         }
         if (g < G && ok) {
           // acc * (1 / l) as the reference does (paged_attention_utils.hpp:834-835);
           // an empty context (l = 0) gives zeros
           const float inv = (l_all > 0.f) ? (1.f / l_all) : 0.f;
-          const size_t head = static_cast<size_t>(first.seq) * args.num_heads + first.kv_head * G + g;
+          const size_t head = static_cast<size_t>(first.seq) * args.num_heads + (first.head_base + hh) * G + g;
           args.out[head * D + d] = __float2half_rn(o_all * args.out_scale * inv);
         }
       }
