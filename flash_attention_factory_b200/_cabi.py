@@ -19,6 +19,8 @@ PA_ERR_BAD_ARG = 2
 PA_ERR_CUDA = 3
 PA_ERR_TIMEOUT = 4
 
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024  # PA_STATIC_SCRATCH_BYTES
+
 _LIB_NAME = "libpaged_attention_b200.so"
 _lib = None
 
@@ -27,6 +29,7 @@ EXPORTED_SYMBOLS = (
     "launch_kernels_reduce",
     "launch_kernels_fp8_loop",
     "launch_kernels_fp8_reduce",
+    "launch_kernels_reduce_static_scratch",
     "pa_query_policy",
     "pa_partition_size",
     "pa_last_error",
@@ -106,6 +109,8 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = launcher_args
         fn.restype = ctypes.c_int
+    lib.launch_kernels_reduce_static_scratch.argtypes = [ctypes.POINTER(PaParams), ctypes.c_void_p]
+    lib.launch_kernels_reduce_static_scratch.restype = ctypes.c_int
     lib.pa_query_policy.argtypes = [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
                                     ctypes.POINTER(PaPolicyInfo)]
     lib.pa_query_policy.restype = ctypes.c_int

@@ -135,6 +135,38 @@ PA_API int launch_kernels_fp8_loop(const pa_params *p, void *stream, float *us_o
  * (paged_attention_fp8_reduce/launch_kernels_fp8_reduce.h:16-76,78-196). */
 PA_API int launch_kernels_fp8_reduce(const pa_params *p, void *stream, float *us_out);
 
+/* Size in bytes of the scratch array built into the library for
+ * launch_kernels_reduce_static_scratch (32 MiB, held by every GPU that loads the library). */
+#define PA_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+
+/* fp16 KV cache, split-context, for callers that cannot allocate device memory.
+ * No counterpart in the reference: there the caller always allocates max_logits,
+ * exp_sums and tem_output itself.
+ *
+ * Same computation and same two kernels as launch_kernels_reduce, but the
+ * per-partition maxima, exp-sums and partial outputs are kept in a fixed
+ * PA_STATIC_SCRATCH_BYTES array inside the library's device image, so a host
+ * that may not call cudaMalloc (memory owned by a foreign pool, allocation
+ * forbidden after start-up, no tolerance for the device-wide synchronisation
+ * an allocation implies) can still run the split variant.  The call itself
+ * allocates nothing, on the device or through any library, and is always
+ * asynchronous on `stream` (no timing, no host synchronisation).
+ *
+ * The caller passes the inputs and `out` as usual; p->max_logits, p->exp_sums
+ * and p->tmp_out are ignored and may be NULL; p->max_num_partitions must still
+ * cover ceil(max context / partition size).  The call fails with
+ * PA_ERR_BAD_ARG, before any work is enqueued, if
+ *   2 * align256(4 * rows) + align256(2 * head_size * rows) > PA_STATIC_SCRATCH_BYTES,
+ *   rows = num_seqs * num_heads * max_num_partitions.
+ *
+ * The first call on each device looks up the array's device address (with
+ * that device current) and caches it; make that first call outside of any
+ * stream capture.  All calls on a device share the one array and it keeps the
+ * previous call's contents: two calls whose kernels overlap on the GPU (other
+ * streams, other host threads) race on it, so serialise them.  Nothing in the
+ * array needs clearing between calls. */
+PA_API int launch_kernels_reduce_static_scratch(const pa_params *p, void *stream);
+
 /* Compile-time policy of include/paged_attention_policy_v2.hpp as data
  * (reference include/paged_attention_policy_v2.hpp:5-100).  Returns
  * PA_ERR_UNSUPPORTED for triples the launchers reject. */
