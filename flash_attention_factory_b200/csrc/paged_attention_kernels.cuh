@@ -343,6 +343,82 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t lm_off_b = swizzled_offset<geo::slab_bytes>(lm_row_b, (lane >> 3) & 1u); // fp16 V
     constexpr uint32_t PAIRS_PER_SLAB = geo::chunks_per_slab / 2;
 
+    // S^T tile of 16 tokens: K (A operand) from shared memory at k_addr, Q from registers;
+    // two accumulation chains shorten the dependency
+    auto score_tile = [&](uint32_t k_addr, const uint32_t (&q)[KSTEPS][2], float (&c)[4]) {
+      float s_a[4] = {0.f, 0.f, 0.f, 0.f};
+      float s_b[4] = {0.f, 0.f, 0.f, 0.f};
+      if constexpr (KV == KV_F16) {
+#pragma unroll
+        for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+          uint32_t a[4];
+          ldmatrix_x4(a, (k_addr ^ ((ks % PAIRS_PER_SLAB) << 5)) + (ks / PAIRS_PER_SLAB) * L::SLAB_TILE);
+          if (ks & 1u) mma_m16n8k16(s_b, a, q[ks][0], q[ks][1]);
+          else mma_m16n8k16(s_a, a, q[ks][0], q[ks][1]);
+        }
+      } else {
+#pragma unroll
+        for (uint32_t qq = 0; qq < KSTEPS / 2; ++qq) {
+          // r[0]/r[1]: rows gid / gid+8 of chunk 2qq, r[2]/r[3]: the same of chunk 2qq+1
+          uint32_t r[4];
+          ldmatrix_x4(r, k_addr ^ (qq << 5));
+          uint32_t a[4];
+          fp8x4_to_half2x2<KV>(r[0], a[0], a[2]);
+          fp8x4_to_half2x2<KV>(r[1], a[1], a[3]);
+          mma_m16n8k16(s_a, a, q[2 * qq][0], q[2 * qq][1]);
+          fp8x4_to_half2x2<KV>(r[2], a[0], a[2]);
+          fp8x4_to_half2x2<KV>(r[3], a[1], a[3]);
+          mma_m16n8k16(s_b, a, q[2 * qq + 1][0], q[2 * qq + 1][1]);
+        }
+      }
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) c[j] = s_a[j] + s_b[j];
+    };
+    // O^T += V^T . P^T for 16 tokens: V (A operand, transposed load) from shared memory
+    auto value_tile = [&](uint32_t v_base, uint32_t p_lo, uint32_t p_hi, float (&o)[KSTEPS][4]) {
+      if constexpr (KV == KV_F16) {
+        const uint32_t v_addr = v_base + lm_off_b;
+#pragma unroll
+        for (uint32_t i = 0; i < KSTEPS; ++i) {
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, (v_addr ^ ((i % PAIRS_PER_SLAB) << 5)) + (i / PAIRS_PER_SLAB) * L::SLAB_TILE);
+          mma_m16n8k16(o[i], a, p_lo, p_hi);
+        }
+      } else {
+        const uint32_t v_addr = v_base + lm_off_a;
+#pragma unroll
+        for (uint32_t qq = 0; qq < KSTEPS / 2; ++qq) {
+          // 16 tokens x 32 dims of bytes, read as transposed 16-bit units:
+          // r[0]: tokens 0-7 / dims 0-15, r[1]: tokens 8-15 / dims 0-15,
+          // r[2]: tokens 0-7 / dims 16-31, r[3]: tokens 8-15 / dims 16-31.
+          // Each register = {V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1]}.
+          uint32_t r[4];
+          ldmatrix_x4_trans(r, v_addr ^ (qq << 5));
+          uint32_t ae[4], ao[4];
+          fp8x4_to_even_odd_half2<KV>(r[0], ae[0], ao[0]);
+          fp8x4_to_even_odd_half2<KV>(r[2], ae[1], ao[1]);
+          fp8x4_to_even_odd_half2<KV>(r[1], ae[2], ao[2]);
+          fp8x4_to_even_odd_half2<KV>(r[3], ae[3], ao[3]);
+          mma_m16n8k16(o[2 * qq], ae, p_lo, p_hi);
+          mma_m16n8k16(o[2 * qq + 1], ao, p_lo, p_hi);
+        }
+      }
+    };
+    // Last tile of a context: clear the V rows past it (unused tail of the last block, or rows
+    // no copy of this stage wrote), so that 0 * garbage stays 0.
+    auto zero_value_rows = [&](uint32_t v_base, uint32_t first_row, uint32_t num_rows, uint32_t ln) {
+      constexpr uint32_t CPR = geo::slab_bytes / 16; // 16-byte chunks per row
+      for (uint32_t sl = 0; sl < geo::num_slabs; ++sl) {
+        for (uint32_t c = ln; c < num_rows * CPR; c += 32) {
+          const uint32_t addr = v_base + sl * L::SLAB_TILE + (first_row + c / CPR) * geo::slab_bytes + (c % CPR) * 16;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+        }
+      }
+      // order these generic-proxy writes before the TMA (async proxy) refill of the slot
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+    };
+
     uint32_t slot = 0, phase = 0, item_parity = 0;
     bool alive = true;
     uint32_t qf[KSTEPS][2];
@@ -380,73 +456,56 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
 
       const uint32_t my_tokens = cur.tok_end - cur.tok_begin;
       const uint32_t my_stages = divide_round_up(my_tokens, tps);
-      for (uint32_t st = 0; st < my_stages; ++st) {
+      // Two stages per iteration: their score tiles are independent instruction streams
+      // (more work in flight per warp) and share one softmax step.
+      for (uint32_t st = 0; st < my_stages; st += 2) {
+        const bool has_b = st + 1 < my_stages;
+        const uint32_t slot_a = slot, phase_a = phase;
+        if (++slot == NSTAGES) {
+          slot = 0;
+          phase ^= 1u;
+        }
+        const uint32_t slot_b = slot, phase_b = phase;
+        if (has_b && ++slot == NSTAGES) {
+          slot = 0;
+          phase ^= 1u;
+        }
         // after an abort the loops keep their shape (the named barriers below need every
         // consumer warp) but no longer wait or compute
-        if (alive) alive = mbar_wait_bounded(&full_bar[slot], phase, abort_flag);
-        const uint32_t tile_tok0 = st * tps + my_slice * 16; // first token of this warp's tile
-        if (alive && tile_tok0 < my_tokens) {
-          const uint32_t n_valid = min(16u, my_tokens - tile_tok0);
-          const uint32_t k_base = ring_base + slot * L::STAGE_BYTES;
-          const uint32_t v_base = k_base + L::KV_TILE;
-          const uint32_t k_addr = k_base + lm_off_a;
-          if (n_valid < 16u) {
-            // Last tile of the context: clear the V rows past it (unused tail of the last
-            // block, or rows no copy of this stage wrote), so that 0 * garbage stays 0.
-            const uint32_t zero_rows = 16u - n_valid;
-            constexpr uint32_t CPR = geo::slab_bytes / 16; // 16-byte chunks per row
-            for (uint32_t sl = 0; sl < geo::num_slabs; ++sl) {
-              for (uint32_t c = lane; c < zero_rows * CPR; c += 32) {
-                const uint32_t row = cw * 16 + n_valid + c / CPR;
-                const uint32_t addr = v_base + sl * L::SLAB_TILE + row * geo::slab_bytes + (c % CPR) * 16;
-                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
-              }
-            }
-            // order these generic-proxy writes before the TMA (async proxy) refill of the slot
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-          }
+        if (alive) alive = mbar_wait_bounded(&full_bar[slot_a], phase_a, abort_flag);
+        if (alive && has_b) alive = mbar_wait_bounded(&full_bar[slot_b], phase_b, abort_flag);
+        const uint32_t tok_a = st * tps + my_slice * 16; // first token of this warp's tile A
+        const uint32_t tok_b = tok_a + tps;
+        if (alive && tok_a < my_tokens) {
+          const bool act_b = has_b && tok_b < my_tokens;
+          const uint32_t n_a = min(16u, my_tokens - tok_a);
+          const uint32_t n_b = act_b ? min(16u, my_tokens - tok_b) : 0u;
+          const uint32_t base_a = ring_base + slot_a * L::STAGE_BYTES;
+          const uint32_t base_b = ring_base + slot_b * L::STAGE_BYTES;
+          if (n_a < 16u) zero_value_rows(base_a + L::KV_TILE, cw * 16 + n_a, 16u - n_a, lane);
+          if (act_b && n_b < 16u) zero_value_rows(base_b + L::KV_TILE, cw * 16 + n_b, 16u - n_b, lane);
 
-          // ---- S^T = K . Q^T  (two accumulation chains shorten the dependency)
-          float s_a[4] = {0.f, 0.f, 0.f, 0.f};
-          float s_b[4] = {0.f, 0.f, 0.f, 0.f};
-          if constexpr (KV == KV_F16) {
-#pragma unroll
-            for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
-              uint32_t a[4];
-              ldmatrix_x4(a, (k_addr ^ ((ks % PAIRS_PER_SLAB) << 5)) + (ks / PAIRS_PER_SLAB) * L::SLAB_TILE);
-              if (ks & 1u) mma_m16n8k16(s_b, a, qf[ks][0], qf[ks][1]);
-              else mma_m16n8k16(s_a, a, qf[ks][0], qf[ks][1]);
-            }
+          // ---- S^T = K . Q^T ; lane holds S[tok gid][g 2t4, 2t4+1] in [0],[1] and
+          // S[tok gid+8][..] in [2],[3]
+          float ca[4], cb[4];
+          score_tile(base_a + lm_off_a, qf, ca);
+          if (act_b) {
+            score_tile(base_b + lm_off_a, qf, cb);
           } else {
-#pragma unroll
-            for (uint32_t q = 0; q < KSTEPS / 2; ++q) {
-              // r[0]/r[1]: rows gid / gid+8 of chunk 2q, r[2]/r[3]: the same of chunk 2q+1
-              uint32_t r[4];
-              ldmatrix_x4(r, k_addr ^ (q << 5));
-              uint32_t a[4];
-              fp8x4_to_half2x2<KV>(r[0], a[0], a[2]);
-              fp8x4_to_half2x2<KV>(r[1], a[1], a[3]);
-              mma_m16n8k16(s_a, a, qf[2 * q][0], qf[2 * q][1]);
-              fp8x4_to_half2x2<KV>(r[2], a[0], a[2]);
-              fp8x4_to_half2x2<KV>(r[3], a[1], a[3]);
-              mma_m16n8k16(s_b, a, qf[2 * q + 1][0], qf[2 * q + 1][1]);
-            }
+            cb[0] = cb[1] = cb[2] = cb[3] = neg_infinity();
           }
-          // lane holds S[tok gid][g 2t4, 2t4+1] in [0],[1] and S[tok gid+8][..] in [2],[3]
-          float c[4];
-#pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) c[j] = s_a[j] + s_b[j];
-          if (n_valid < 16u) {
+          if (n_a < 16u || (act_b && n_b < 16u)) {
             // tokens past the context never count, whatever the cache holds there
             // (reference paged_attention_kernel_loop.hpp:323-327)
-            if (gid >= n_valid) c[0] = c[1] = neg_infinity();
-            if (gid + 8 >= n_valid) c[2] = c[3] = neg_infinity();
+            if (gid >= n_a) ca[0] = ca[1] = neg_infinity();
+            if (gid + 8 >= n_a) ca[2] = ca[3] = neg_infinity();
+            if (gid >= n_b) cb[0] = cb[1] = neg_infinity();
+            if (gid + 8 >= n_b) cb[2] = cb[3] = neg_infinity();
           }
           // ---- online softmax (reference paged_attention_kernel_loop.hpp:382-419);
           // scale > 0, so the maximum commutes with the scaling
-          m_true[0] = fmaxf(m_true[0], quad_column_max(fmaxf(c[0], c[2])) * scale);
-          m_true[1] = fmaxf(m_true[1], quad_column_max(fmaxf(c[1], c[3])) * scale);
+          m_true[0] = fmaxf(m_true[0], quad_column_max(fmaxf(fmaxf(ca[0], ca[2]), fmaxf(cb[0], cb[2]))) * scale);
+          m_true[1] = fmaxf(m_true[1], quad_column_max(fmaxf(fmaxf(ca[1], ca[3]), fmaxf(cb[1], cb[3]))) * scale);
           const bool stale = (m_true[0] > m_ref[0] + kRescaleThreshold) ||
                              (m_true[1] > m_ref[1] + kRescaleThreshold);
           if (__any_sync(0xffffffffu, stale)) {
@@ -464,51 +523,32 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
             m_ref[0] = m_true[0];
             m_ref[1] = m_true[1];
           }
-          const float p0 = fast_exp2(fmaf(c[0], scale, -m_ref[0]));
-          const float p1 = fast_exp2(fmaf(c[1], scale, -m_ref[1]));
-          const float p2 = fast_exp2(fmaf(c[2], scale, -m_ref[0]));
-          const float p3 = fast_exp2(fmaf(c[3], scale, -m_ref[1]));
-          l_run[0] += p0 + p2; // fp32 sum of the unrounded weights
-          l_run[1] += p1 + p3;
-          // P rounded to fp16 for the MMA, transposed into the B-operand layout
-          const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1)); // tokens 0..7
-          const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3)); // tokens 8..15
-
+          float pa[4], pb[4];
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            pa[j] = fast_exp2(fmaf(ca[j], scale, -m_ref[j & 1u]));
+            pb[j] = fast_exp2(fmaf(cb[j], scale, -m_ref[j & 1u]));
+          }
+          l_run[0] += (pa[0] + pa[2]) + (pb[0] + pb[2]); // fp32 sum of the unrounded weights
+          l_run[1] += (pa[1] + pa[3]) + (pb[1] + pb[3]);
+          // P rounded to fp16 for the MMA, transposed into the B-operand layout;
           // ---- O^T += V^T . P^T
-          if constexpr (KV == KV_F16) {
-            const uint32_t v_addr = v_base + lm_off_b;
-#pragma unroll
-            for (uint32_t i = 0; i < KSTEPS; ++i) {
-              uint32_t a[4];
-              ldmatrix_x4_trans(a, (v_addr ^ ((i % PAIRS_PER_SLAB) << 5)) + (i / PAIRS_PER_SLAB) * L::SLAB_TILE);
-              mma_m16n8k16(acc[i], a, pb0, pb1);
-            }
-          } else {
-            const uint32_t v_addr = v_base + lm_off_a;
-#pragma unroll
-            for (uint32_t q = 0; q < KSTEPS / 2; ++q) {
-              // 16 tokens x 32 dims of bytes, read as transposed 16-bit units:
-              // r[0]: tokens 0-7 / dims 0-15, r[1]: tokens 8-15 / dims 0-15,
-              // r[2]: tokens 0-7 / dims 16-31, r[3]: tokens 8-15 / dims 16-31.
-              // Each register = {V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1]}.
-              uint32_t r[4];
-              ldmatrix_x4_trans(r, v_addr ^ (q << 5));
-              uint32_t ae[4], ao[4];
-              fp8x4_to_even_odd_half2<KV>(r[0], ae[0], ao[0]);
-              fp8x4_to_even_odd_half2<KV>(r[2], ae[1], ao[1]);
-              fp8x4_to_even_odd_half2<KV>(r[1], ae[2], ao[2]);
-              fp8x4_to_even_odd_half2<KV>(r[3], ae[3], ao[3]);
-              mma_m16n8k16(acc[2 * q], ae, pb0, pb1);
-              mma_m16n8k16(acc[2 * q + 1], ao, pb0, pb1);
-            }
+          {
+            const uint32_t p_lo = movmatrix_trans(pack_half2(pa[0], pa[1])); // tokens 0..7
+            const uint32_t p_hi = movmatrix_trans(pack_half2(pa[2], pa[3])); // tokens 8..15
+            value_tile(base_a + L::KV_TILE, p_lo, p_hi, acc);
+          }
+          if (act_b) {
+            const uint32_t p_lo = movmatrix_trans(pack_half2(pb[0], pb[1]));
+            const uint32_t p_hi = movmatrix_trans(pack_half2(pb[2], pb[3]));
+            value_tile(base_b + L::KV_TILE, p_lo, p_hi, acc);
           }
         }
-        // this warp is done with the stage: let the producer refill it
+        // this warp is done with the stages: let the producer refill them
         __syncwarp();
-        if (alive && lane == 0) mbar_arrive(&empty_bar[slot]);
-        if (++slot == NSTAGES) {
-          slot = 0;
-          phase ^= 1u;
+        if (alive && lane == 0) {
+          mbar_arrive(&empty_bar[slot_a]);
+          if (has_b) mbar_arrive(&empty_bar[slot_b]);
         }
       }
 
