@@ -279,6 +279,10 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kv", default=None, choices=["float16", "float8_e5m2", "float8_e4m3fn"],
                     help="override the KV cache type of the configuration")
+    ap.add_argument("--head-size", type=int, default=None, choices=[64, 128])
+    ap.add_argument("--heads", type=int, default=None, help="override the number of query heads")
+    ap.add_argument("--kv-heads", type=int, default=None, help="override the number of KV heads")
+    ap.add_argument("--block-size", type=int, default=None, choices=[16, 32, 64, 128])
     ap.add_argument("--num-seqs", type=int, default=None,
                     help="override the number of sequences (small cases for profiler captures)")
     a = ap.parse_args()
@@ -292,6 +296,10 @@ def main() -> None:
         spec["num_seqs"] = a.num_seqs
     if a.kv is not None:
         spec["kv"] = a.kv
+    for key, val in (("head_size", a.head_size), ("heads", a.heads), ("kv_heads", a.kv_heads),
+                     ("block_size", a.block_size)):
+        if val is not None:
+            spec[key] = val
     variant = a.variant or pick_variant(spec)
 
     if a.impl == "reference":
@@ -394,8 +402,8 @@ def main() -> None:
             "dtype": "f16 x f16 -> f32 (mma.sync), KV stored as " + spec["kv"], "data": "synthetic",
             "config": {"workload": f"BASELINE config {a.config[1]}: {variant} variant, KV {spec['kv']}, "
                                    f"num_seqs={spec['num_seqs']}{' per GPU' if not strong and world > 1 else ''}, "
-                                   f"heads={spec['heads']}/{spec['kv_heads']}, head_size=128, block_size=16, "
-                                   f"ctx={spec['ctx']}",
+                                   f"heads={spec['heads']}/{spec['kv_heads']}, head_size={spec['head_size']}, "
+                                   f"block_size={spec['block_size']}, ctx={spec['ctx']}",
                        "entry_point": f"launch_kernels_{'fp8_' if w.fp8 else ''}{variant}",
                        "kv_bytes_per_call_per_gpu": w.kv_bytes, "cache_copies_rotated": w.copies,
                        "l2_policy": "inputs larger than L2" if w.copies == 1 else

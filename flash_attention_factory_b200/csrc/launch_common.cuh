@@ -8,6 +8,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "paged_attention_b200.h"
@@ -33,25 +34,37 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn get_encode_tiled(); // defined in c_api.cu; nullptr if the driver lacks it
 
-// Describes one cache tensor [num_blocks*block_size rows, num_kv_heads*head_size elems]
-// with a box of (slab_elems x rows_per_box); rows past num_blocks*block_size read as zero.
+// Describes one cache tensor to the TMA unit as (head dim, token row, KV head): extents
+// (head_size, num_blocks*block_size, num_kv_heads), strides (1 elem, num_kv_heads*head_size
+// elems, head_size elems).  A box is (one 128-byte slab, rows_per_box rows, heads_per_box
+// heads) and lands in shared memory as [head][row][slab]; rows past the cache read as zero.
 template <int D, int KV>
-int encode_cache_map(CUtensorMap *map, const void *cache, const pa_params *p, uint32_t rows_per_box) {
+int encode_cache_map(CUtensorMap *map, const void *cache, const pa_params *p, uint32_t rows_per_box,
+                     uint32_t heads_per_box) {
   using geo = kv_tile_geometry<D, KV>;
   EncodeTiledFn encode = get_encode_tiled();
   if (encode == nullptr) return fail(PA_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(p->num_kv_heads) * D,
-                              static_cast<cuuint64_t>(p->num_blocks) * p->block_size};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p->num_kv_heads) * D * geo::elt_bytes};
-  const cuuint32_t box[2] = {geo::slab_elems, rows_per_box};
-  const cuuint32_t elem_strides[2] = {1, 1};
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(p->num_blocks) * p->block_size,
+                              static_cast<cuuint64_t>(p->num_kv_heads)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(p->num_kv_heads) * D * geo::elt_bytes,
+                                 static_cast<cuuint64_t>(D) * geo::elt_bytes};
+  const cuuint32_t box[3] = {geo::slab_elems, rows_per_box, heads_per_box};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
   const CUtensorMapDataType dt =
       (KV == KV_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const CUtensorMapSwizzle sw =
       (geo::slab_bytes == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-  const CUresult r = encode(map, dt, 2, const_cast<void *>(cache), dims, strides, box, elem_strides,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  // debugging knob: PA_TMA_L2_PROMOTION=0..3 (none, 64 B, 128 B, 256 B); default 256 B
+  static const int promo = [] {
+    const char *e = std::getenv("PA_TMA_L2_PROMOTION");
+    return (e != nullptr && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 3;
+  }();
+  const CUtensorMapL2promotion l2 = promo == 0   ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                                    : promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                    : promo == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                 : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+  const CUresult r = encode(map, dt, 3, const_cast<void *>(cache), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, l2, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(PA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return PA_OK;
 }
@@ -155,6 +168,8 @@ AttnArgs make_attn_args(const pa_params *p) {
   a.tokens_per_stage = policy::tokens_per_stage / a.hpc;
   a.rows_per_box = p->block_size < a.tokens_per_stage ? p->block_size : a.tokens_per_stage;
   a.boxes_per_stage = a.hpc * (a.tokens_per_stage / a.rows_per_box);
+  // one TMA box spans all of the CTA's heads when a box fills the stage's rows of a head
+  a.heads_per_box = (a.rows_per_box == a.tokens_per_stage) ? a.hpc : 1u;
   const float kv_scale = (KV == KV_F16) ? 1.f : p->fp8_scale;
   // the FP8 scale is applied once, hoisted out of the dot products
   // (reference paged_attention_kernel_fp8_loop.hpp:333,545)
@@ -174,8 +189,8 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
 
   AttnArgs args = make_attn_args<D, KV>(p);
   CUtensorMap map_k, map_v;
-  if (int rc = encode_cache_map<D, KV>(&map_k, p->key_cache, p, args.rows_per_box)) return rc;
-  if (int rc = encode_cache_map<D, KV>(&map_v, p->value_cache, p, args.rows_per_box)) return rc;
+  if (int rc = encode_cache_map<D, KV>(&map_k, p->key_cache, p, args.rows_per_box, args.heads_per_box)) return rc;
+  if (int rc = encode_cache_map<D, KV>(&map_v, p->value_cache, p, args.rows_per_box, args.heads_per_box)) return rc;
 
   auto kernel = paged_attention_kernel<D, KV, MODE>;
   static thread_local int configured_device = -1;
@@ -192,10 +207,10 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
   cfg.dynamicSmemBytes = L::DYN_SMEM;
   cfg.stream = stream;
   if (MODE == MODE_SPLIT) {
-    // persistent CTAs, two per SM, each walking the (seq, partition, kv head) items with
+    // persistent CTAs, as many as fit on the device, each walking the (seq, partition, kv head) items with
     // stride gridDim.x; the TMA ring keeps streaming across item boundaries
     const uint64_t items = static_cast<uint64_t>(p->num_kv_heads / args.hpc) * p->max_num_partitions * p->num_seqs;
-    const uint64_t resident = 2ull * static_cast<uint64_t>(dev.sm_count);
+    const uint64_t resident = static_cast<uint64_t>(policy::ctas_per_sm) * static_cast<uint64_t>(dev.sm_count);
     cfg.gridDim = dim3(static_cast<unsigned>(items < resident ? items : resident), 1, 1);
     cfg.numAttrs = 0;
   } else {
@@ -215,10 +230,23 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
 template <int D>
 int enqueue_merge(const pa_params *p, cudaStream_t stream) {
   const uint32_t psize = (D == 64) ? 256u : 512u;
-  merge_partitions_kernel<D><<<dim3(p->num_heads, p->num_seqs), 128, 0, stream>>>(
-      static_cast<__half *>(p->out), static_cast<const __half *>(p->tmp_out), p->max_logits,
-      p->exp_sums, p->context_lens, p->num_heads, p->max_num_partitions, psize);
-  PA_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  cfg.gridDim = dim3(p->num_heads, p->num_seqs, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  // programmatic dependent launch: the CTAs are scheduled while the attention kernel drains
+  // and block in griddepcontrol.wait until that kernel has completed
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partitions_kernel<D>, static_cast<__half *>(p->out),
+                                 static_cast<const __half *>(p->tmp_out),
+                                 static_cast<const float *>(p->max_logits),
+                                 static_cast<const float *>(p->exp_sums), p->context_lens, p->num_heads,
+                                 p->max_num_partitions, psize));
   return PA_OK;
 }
 

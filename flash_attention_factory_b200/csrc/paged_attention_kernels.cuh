@@ -14,7 +14,8 @@
 // (reference paged_attention_reduce, paged_attention_kernel_v2.hpp:594-970).
 //
 // Structure of the attention kernel: warp 0 walks the block table and issues
-// tiled TMA copies (one box per KV block, KV head and 128-byte slab) into a
+// tiled TMA copies (one box per KV block and 128-byte slab, spanning the CTA's KV heads
+// where a block fills the stage) into a
 // ring of shared-memory stages guarded by full/empty mbarriers; warps 1..4
 // each own 16 rows of every stage.  A CTA works on `hpc` (1, 2 or 4)
 // neighbouring KV heads at once: with hpc = 4 a warp owns one KV head and sees
@@ -66,6 +67,7 @@ struct AttnArgs {
   uint32_t tokens_per_stage; // 64 / hpc
   uint32_t rows_per_box;     // min(block_size, tokens_per_stage)
   uint32_t boxes_per_stage;  // hpc * tokens_per_stage / rows_per_box: 1, 2 or 4
+  uint32_t heads_per_box;    // KV heads one TMA box covers: hpc if rows_per_box == tokens_per_stage, else 1
   float scale_log2;          // sm_scale * fp8_scale * log2(e), > 0
   float out_scale;           // fp8_scale (1 for fp16)
 };
@@ -184,7 +186,8 @@ __device__ __forceinline__ void load_q_fragments(uint32_t (&qf)[D / 16][2], cons
 }
 
 template <int D, int KV, int MODE>
-__global__ void __launch_bounds__(paged_attention_policy_v2<D, KV>::threads_per_cta, 2)
+__global__ void __launch_bounds__(paged_attention_policy_v2<D, KV>::threads_per_cta,
+                                  paged_attention_policy_v2<D, KV>::ctas_per_sm)
 paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const AttnArgs args) {
   using L = SmemLayout<D, KV>;
@@ -216,6 +219,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   uint32_t cta_rank = 0, num_ranks = 1;
   WorkItem first{};
   if constexpr (MODE == MODE_SPLIT) {
+    // let the merge kernel's CTAs be scheduled as this grid's CTAs retire (it waits for the
+    // completion of this grid before it reads anything)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     first = find_split_item<policy::partition_size>(blockIdx.x, args);
   } else {
     namespace cg = cooperative_groups;
@@ -278,7 +284,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       if constexpr (MODE == MODE_SPLIT)
         nxt = find_split_item<policy::partition_size>(cur.linear + gridDim.x, args);
       const uint32_t total_chunks = divide_round_up(cur.tok_end - cur.tok_begin, rows);
-      const int32_t x0 = static_cast<int32_t>((cur.head_base + lane_head) * D);
+      const int32_t head_coord = static_cast<int32_t>(cur.head_base + lane_head);
       for (uint32_t chunk0 = 0; chunk0 < total_chunks && alive; chunk0 += chunks_per_batch) {
         const uint32_t chunk = chunk0 + lane_chunk;
         const uint32_t block_id = block_id_next;
@@ -301,16 +307,17 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           }
           alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
           if (!alive) break;
-          if (valid && lane_chunk / chunks_per_stage == sb) {
-            // rows of a stage: head-major, tokens_per_stage rows per head
+          if (valid && lane_chunk / chunks_per_stage == sb && lane_head % args.heads_per_box == 0) {
+            // rows of a stage: head-major, tokens_per_stage rows per head; a box that spans
+            // several heads lands as [head][row][slab], which is this very layout
             const uint32_t row0 = lane_head * tps + (lane_chunk % chunks_per_stage) * rows;
             const uint32_t stage_base = ring_base + slot * L::STAGE_BYTES;
 #pragma unroll
             for (uint32_t sl = 0; sl < geo::num_slabs; ++sl) {
               const uint32_t dst = stage_base + sl * L::SLAB_TILE + row0 * geo::slab_bytes;
-              const int32_t x = x0 + static_cast<int32_t>(sl * geo::slab_elems);
-              tma_load_2d(dst, &tmap_k, &full_bar[slot], x, y);
-              tma_load_2d(dst + L::KV_TILE, &tmap_v, &full_bar[slot], x, y);
+              const int32_t x = static_cast<int32_t>(sl * geo::slab_elems);
+              tma_load_3d(dst, &tmap_k, &full_bar[slot], x, y, head_coord);
+              tma_load_3d(dst + L::KV_TILE, &tmap_v, &full_bar[slot], x, y, head_coord);
             }
           }
           if (++slot == NSTAGES) {
@@ -775,24 +782,42 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
 //   out[d] = sum_p (w_p / W) * tmp_out[p, d]
 // over the partitions p < ceil(ctx / partition_size) only
 // (reference paged_attention_kernel_v2.hpp:679,736-764,813-863,924-932).
+// Latency-bound: the partial-output rows are requested before the weights are known, four
+// rows per warp in flight, so that a typical call costs little more than one memory round trip.
 template <int D>
 __global__ void __launch_bounds__(128)
 merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp_out,
                         const float *__restrict__ max_logits, const float *__restrict__ exp_sums,
                         const uint32_t *__restrict__ context_lens, uint32_t num_heads,
                         uint32_t max_num_partitions, uint32_t partition_size) {
-  constexpr uint32_t LANES_PER_ROW = D / 4; // each lane owns 4 dims (8 bytes)
-  constexpr uint32_t ROWS = 128 / LANES_PER_ROW; // partitions handled in parallel
+  constexpr uint32_t LANES_PER_ROW = D / 4;         // each lane owns 4 dims (8 bytes)
+  constexpr uint32_t ROWS = 128 / LANES_PER_ROW;    // partitions handled in parallel
+  constexpr uint32_t UNROLL = 4;                    // rows in flight per thread
+  constexpr uint32_t WEIGHT_CACHE = 1024;           // weights kept in shared memory
   const uint32_t head = blockIdx.x;
   const uint32_t seq = blockIdx.y;
   const uint32_t tid = threadIdx.x;
+  // Launched with programmatic stream serialization, this grid may start while the attention
+  // kernel drains; nothing is read before that kernel has completed and its writes are visible.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t ctx = context_lens[seq];
   const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
   const size_t base = (static_cast<size_t>(seq) * num_heads + head) * max_num_partitions;
   __half *orow = out + (static_cast<size_t>(seq) * num_heads + head) * D;
 
   __shared__ float red[4];
+  __shared__ float weights[WEIGHT_CACHE];
   __shared__ float part[ROWS][D];
+
+  const uint32_t row = tid / LANES_PER_ROW;
+  const uint32_t col = (tid % LANES_PER_ROW) * 4;
+  // first UNROLL rows of this thread: requested now, used after the weights are ready
+  uint2 raw[UNROLL];
+#pragma unroll
+  for (uint32_t u = 0; u < UNROLL; ++u) {
+    const uint32_t p = row + u * ROWS;
+    raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint2 *>(tmp_out + (base + p) * D + col)) : make_uint2(0u, 0u);
+  }
 
   // global max over partitions
   float m = neg_infinity();
@@ -803,28 +828,49 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
   __syncthreads();
   m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
   __syncthreads();
-  // total rescaled weight
+  // rescaled weights and their total
   float wsum = 0.f;
-  for (uint32_t p = tid; p < np; p += 128) wsum += exp_sums[base + p] * __expf(max_logits[base + p] - m);
+  for (uint32_t p = tid; p < np; p += 128) {
+    const float w = exp_sums[base + p] * __expf(max_logits[base + p] - m);
+    if (p < WEIGHT_CACHE) weights[p] = w;
+    wsum += w;
+  }
 #pragma unroll
   for (uint32_t o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
   if ((tid & 31u) == 0) red[tid >> 5] = wsum;
   __syncthreads();
   wsum = red[0] + red[1] + red[2] + red[3];
   const float inv_w = (wsum > 0.f) ? 1.f / wsum : 0.f;
+  auto weight_of = [&](uint32_t p) -> float {
+    return (p < WEIGHT_CACHE) ? weights[p] : exp_sums[base + p] * __expf(max_logits[base + p] - m);
+  };
 
-  const uint32_t row = tid / LANES_PER_ROW;
-  const uint32_t col = (tid % LANES_PER_ROW) * 4;
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  for (uint32_t p = row; p < np; p += ROWS) {
-    const float w = exp_sums[base + p] * __expf(max_logits[base + p] - m) * inv_w;
-    const uint2 raw = *reinterpret_cast<const uint2 *>(tmp_out + (base + p) * D + col);
-    const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-    const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+  auto accumulate = [&](uint2 v, float w) {
+    const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
+    const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
     a0 += w * v01.x;
     a1 += w * v01.y;
     a2 += w * v23.x;
     a3 += w * v23.y;
+  };
+  // partitions are taken in increasing order per thread: the sum has a fixed order
+#pragma unroll
+  for (uint32_t u = 0; u < UNROLL; ++u) {
+    const uint32_t p = row + u * ROWS;
+    if (p < np) accumulate(raw[u], weight_of(p) * inv_w);
+  }
+  for (uint32_t p0 = row + UNROLL * ROWS; p0 < np; p0 += UNROLL * ROWS) {
+#pragma unroll
+    for (uint32_t u = 0; u < UNROLL; ++u) {
+      const uint32_t p = p0 + u * ROWS;
+      raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint2 *>(tmp_out + (base + p) * D + col)) : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (uint32_t u = 0; u < UNROLL; ++u) {
+      const uint32_t p = p0 + u * ROWS;
+      if (p < np) accumulate(raw[u], weight_of(p) * inv_w);
+    }
   }
   part[row][col] = a0;
   part[row][col + 1] = a1;

@@ -215,6 +215,15 @@ PA_DEV void tma_load_2d(uint32_t dst_smem, const void *tensor_map, uint64_t *bar
       "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// Tiled 3-D copy global -> this CTA's shared memory, completion on `bar`.
+PA_DEV void tma_load_3d(uint32_t dst_smem, const void *tensor_map, uint64_t *bar, int32_t x,
+                        int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst_smem),
+      "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 PA_DEV void tma_prefetch_descriptor(const void *tensor_map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensor_map)) : "memory");
 }
