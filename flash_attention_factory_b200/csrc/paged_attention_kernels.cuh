@@ -483,6 +483,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         if (alive && has_b) alive = mbar_wait_bounded(&full_bar[slot_b], phase_b, abort_flag);
         const uint32_t tok_a = st * tps + my_slice * 16; // first token of this warp's tile A
         const uint32_t tok_b = tok_a + tps;
+        bool released_a = false;
         if (alive && tok_a < my_tokens) {
           const bool act_b = has_b && tok_b < my_tokens;
           const uint32_t n_a = min(16u, my_tokens - tok_a);
@@ -545,6 +546,12 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
             const uint32_t p_hi = movmatrix_trans(pack_half2(pa[2], pa[3])); // tokens 8..15
             value_tile(base_a + L::KV_TILE, p_lo, p_hi, acc);
           }
+          if (has_b) {
+            // stage A is no longer needed: hand it back before working on stage B
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[slot_a]);
+            released_a = true;
+          }
           if (act_b) {
             const uint32_t p_lo = movmatrix_trans(pack_half2(pb[0], pb[1]));
             const uint32_t p_hi = movmatrix_trans(pack_half2(pb[2], pb[3]));
@@ -554,7 +561,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         // this warp is done with the stages: let the producer refill them
         __syncwarp();
         if (alive && lane == 0) {
-          mbar_arrive(&empty_bar[slot_a]);
+          if (!released_a) mbar_arrive(&empty_bar[slot_a]);
           if (has_b) mbar_arrive(&empty_bar[slot_b]);
         }
       }

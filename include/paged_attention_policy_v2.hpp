@@ -54,14 +54,12 @@ struct paged_attention_policy_v2 : paged_attention_base_policy {
   static constexpr uint32_t tokens_per_stage = consumer_warps * tokens_per_warp; // 64
   static constexpr uint32_t threads_per_cta = (consumer_warps + 1) * 32; // + 1 TMA warp
   static constexpr uint32_t stage_bytes = 2u * tokens_per_stage * geometry::row_bytes; // K + V
-  // CTAs per SM and ring depth: fp16 stages are 32 KB (head 128), so two CTAs with a 96 KB
-  // ring share an SM; FP8 needs twice the instructions per byte, so three CTAs (12 MMA
-  // warps per SM) with a 64 KB ring each hide its latency better.
-#ifndef PA_FP8_CTAS_PER_SM
-#define PA_FP8_CTAS_PER_SM 3
-#endif
-  static constexpr uint32_t ctas_per_sm = (kv_type_ == KV_F16) ? 2u : PA_FP8_CTAS_PER_SM;
-  static constexpr uint32_t ring_budget = (ctas_per_sm == 2u ? 96u : 64u) * 1024u;
+  // Two CTAs per SM, each with a ring of about 96 KB (3 stages of 32 KB for fp16 / head 128,
+  // 6 stages of 16 KB for FP8).  Measured on B200: three CTAs with 64 KB rings were no faster
+  // for FP8 (the kernel is bound by HBM and by the depth of the ring, not by issue slots) and
+  // left the loop variant with too shallow a ring per CTA.
+  static constexpr uint32_t ctas_per_sm = 2u;
+  static constexpr uint32_t ring_budget = 96u * 1024u;
   static constexpr uint32_t ring_stages_raw = ring_budget / stage_bytes;
   static constexpr uint32_t ring_stages = ring_stages_raw > 8u ? 8u : ring_stages_raw;
   static_assert(ring_stages >= 2, "ring too shallow");
