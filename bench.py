@@ -181,7 +181,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -300,6 +300,7 @@ def main() -> None:
                      ("block_size", a.block_size)):
         if val is not None:
             spec[key] = val
+    overridden = any(v is not None for v in (a.num_seqs, a.kv, a.head_size, a.heads, a.kv_heads, a.block_size))
     variant = a.variant or pick_variant(spec)
 
     if a.impl == "reference":
@@ -417,7 +418,7 @@ def main() -> None:
                          "frac_of_8TBps": round(achieved / NOMINAL_HBM_GBS, 4),
                          "kernel_us": round(attn_mean_us, 2),
                          "merge_kernel_us": round(statistics.mean(merge_us), 2) if merge_us else None,
-                         "traffic": TRAFFIC_BYTES.get((a.config, variant))},
+                         "traffic": TRAFFIC_BYTES.get((a.config, variant)) if not overridden else None},
             "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": w.h2d_bytes,
                     "d2h_bytes_per_step": w.d2h_bytes, "us_per_call": round(ms_e2e / a.steps * 1e3, 2)},
             "gpu_launches": a.steps * w.launches_per_step,
@@ -433,7 +434,12 @@ def main() -> None:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch, from the ncu
 # captures summarised under profiles/ (None until a capture exists for the workload)
-TRAFFIC_BYTES: dict = {}
+TRAFFIC_BYTES: dict = {
+    # profiles/paged_attention_kernel_split_fp16_c2_small.md: 16 x (268.53 + 4.20) MB
+    ("c2", "reduce"): 4_363_700_000,
+    # profiles/paged_attention_kernel_split_e4m3_c4_small.md: 8 x (134.31 + 4.09) MB
+    ("c4", "reduce"): 1_107_200_000,
+}
 
 
 def cpu_baseline(w: Workload) -> dict:
