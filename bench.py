@@ -150,8 +150,27 @@ class Workload:
         a += [self.spec["block_size"], self.max_ctx, self.alibi, None, -1.0]
         return a
 
+    def enqueue(self, step: int, q=None, bt=None, cl=None) -> None:
+        """One asynchronous call of the operator on the current stream."""
+        if self.variant != "auto":
+            self.module().enqueue(*self.args(step, q, bt, cl))
+            return
+        from flash_attention_factory_b200.serving import AutoDecodePlan, paged_attention_auto
+
+        if getattr(self, "plan", None) is None:
+            self.plan = AutoDecodePlan(self.ctx.tolist(), self.spec["heads"], self.spec["head_size"],
+                                       self.spec["block_size"], self.bt.size(1), self.device)
+        i = step % self.copies
+        paged_attention_auto(self.plan, self.out, self.q if q is None else q, self.k[i], self.v[i],
+                             self.bt if bt is None else bt, self.cl if cl is None else cl, self.group,
+                             self.sm_scale, self.fp8_scale)
+
     @property
     def launches_per_step(self) -> int:
+        if self.variant == "auto":
+            plan = getattr(self, "plan", None)
+            return (1 if plan is None or plan.loop is not None else 0) + \
+                   (2 if plan is None or plan.reduce is not None else 0)
         return 2 if self.variant == "reduce" else 1
 
 
@@ -263,8 +282,34 @@ def measured_hbm_peak() -> tuple[float, str]:
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def describe_config(a, spec: dict, variant: str, world: int, ctx) -> dict:
+    """The `config` object of the JSON line; identical for the two --impl arms."""
+    strong = a.config == "c5"
+    fp8 = spec["kv"] != "float16"
+    elt = 1 if fp8 else 2
+    bs = spec["block_size"]
+    blocks = sum((int(c) + bs - 1) // bs for c in ctx.tolist())
+    cache_bytes = 2 * max(1, blocks) * bs * spec["kv_heads"] * spec["head_size"] * elt
+    copies = 1 if cache_bytes >= 4 * L2_BYTES else min(50, math.ceil(4 * L2_BYTES / cache_bytes))
+    kv_bytes = int(ctx.to(torch.int64).sum()) * spec["kv_heads"] * spec["head_size"] * 2 * elt
+    return {
+        "workload": f"BASELINE config {a.config[1]}: {variant} variant, KV {spec['kv']}, "
+                    f"num_seqs={spec['num_seqs']}{' per GPU' if not strong and world > 1 else ''}, "
+                    f"heads={spec['heads']}/{spec['kv_heads']}, head_size={spec['head_size']}, "
+                    f"block_size={spec['block_size']}, ctx={spec['ctx']}",
+        "entry_point": (f"launch_kernels_{'fp8_' if fp8 else ''}{variant}" if variant != "auto" else
+                        f"launch_kernels_{'fp8_' if fp8 else ''}loop + launch_kernels_{'fp8_' if fp8 else ''}reduce, "
+                        "chosen per sequence (serving.paged_attention_auto)"),
+        "kv_bytes_per_call_per_gpu": kv_bytes, "cache_copies_rotated": copies,
+        "l2_policy": "inputs larger than L2" if copies == 1 else
+                     f"rotating over {copies} cache copies (> 4x L2 in total)",
+        "sharding": "none" if world == 1 else
+                    ("sequences split by cumulative KV length" if strong else "one shard per GPU"),
+    }
+
+
 def pick_variant(spec: dict) -> str:
-    return "reduce" if spec["variant"] == "auto" else spec["variant"]
+    return spec["variant"]
 
 
 def main() -> None:
@@ -273,7 +318,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
-    ap.add_argument("--variant", default=None, choices=["loop", "reduce"],
+    ap.add_argument("--variant", default=None, choices=["loop", "reduce", "auto"],
                     help="override the entry point the configuration names")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -324,7 +369,6 @@ def main() -> None:
     strong = a.config == "c5"
     ctx = shard_by_kv_length(ctx_all, world, rank) if (strong and world > 1) else ctx_all
     w = Workload(spec, ctx, device, seed=1000 * int(a.config[1]) + rank, variant=variant)
-    mod = w.module()
 
     def sync_all():
         torch.cuda.synchronize(device)
@@ -334,7 +378,7 @@ def main() -> None:
 
     # ---- device-resident throughput: K asynchronous calls between two events
     for i in range(a.warmup):
-        mod.enqueue(*w.args(i))
+        w.enqueue(i)
     sync_all()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -342,25 +386,28 @@ def main() -> None:
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(a.steps):
-        mod.enqueue(*w.args(i))
+        w.enqueue(i)
     e1.record()
     sync_all()
     ms_total = e0.elapsed_time(e1)
 
     # ---- per-kernel durations (blocking form: events around each kernel)
     attn_us, merge_us = [], []
-    for i in range(min(a.steps, 30)):
-        t = mod.run(*w.args(i))
-        attn_us.append(t[0])
-        if len(t) > 1:
-            merge_us.append(t[1])
+    if variant == "auto":
+        attn_us = [ms_total / a.steps * 1e3]  # two kernels on two streams: the call is the unit
+    else:
+        for i in range(min(a.steps, 30)):
+            t = w.module().run(*w.args(i))
+            attn_us.append(t[0])
+            if len(t) > 1:
+                merge_us.append(t[1])
 
     # ---- end to end: host buffers in, host buffer out, every step
     def e2e_step(i):
         q = w.q_host.to(device, non_blocking=True)
         bt = w.bt_host.to(device, non_blocking=True)
         cl = w.ctx_host.to(device, non_blocking=True)
-        mod.enqueue(*w.args(i, q, bt, cl))
+        w.enqueue(i, q, bt, cl)
         w.out_host.copy_(w.out, non_blocking=True)
         torch.cuda.current_stream(device).synchronize()  # the caller reads the result now
 
@@ -401,16 +448,7 @@ def main() -> None:
             "us_per_call": round(ms_per_step * 1e3, 2), "higher_is_better": True,
             "scaling": "strong" if strong else "weak", "vs_baseline": None,
             "dtype": "f16 x f16 -> f32 (mma.sync), KV stored as " + spec["kv"], "data": "synthetic",
-            "config": {"workload": f"BASELINE config {a.config[1]}: {variant} variant, KV {spec['kv']}, "
-                                   f"num_seqs={spec['num_seqs']}{' per GPU' if not strong and world > 1 else ''}, "
-                                   f"heads={spec['heads']}/{spec['kv_heads']}, head_size={spec['head_size']}, "
-                                   f"block_size={spec['block_size']}, ctx={spec['ctx']}",
-                       "entry_point": f"launch_kernels_{'fp8_' if w.fp8 else ''}{variant}",
-                       "kv_bytes_per_call_per_gpu": w.kv_bytes, "cache_copies_rotated": w.copies,
-                       "l2_policy": "inputs larger than L2" if w.copies == 1 else
-                                    f"rotating over {w.copies} cache copies (> 4x L2 in total)",
-                       "sharding": "none" if world == 1 else
-                                   ("sequences split by cumulative KV length" if strong else "one shard per GPU")},
+            "config": describe_config(a, spec, variant, world, ctx_all),
             "pct_of_8TBps": round(100 * value / (NOMINAL_HBM_GBS * world), 2),
             "roofline": {"bound": "hbm", "kernel": "paged_attention_kernel",
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
@@ -449,10 +487,13 @@ def cpu_baseline(w: Workload) -> dict:
     n = max(1, min(w.num_seqs, int(15.0 / max(t1, 1e-3))))
     sample = cpu_sample_inputs(w, n)
     t = time_cpu_oracle(sample)
-    return {"value": round(sample_kv_bytes(sample, w) / t / 1e9, 4), "unit": "GB/s",
+    reps = 1 + max(0, min(20, int(10.0 / max(t, 1e-3)) - 1))
+    for _ in range(reps - 1):
+        t += time_cpu_oracle(sample)
+    return {"value": round(reps * sample_kv_bytes(sample, w) / t / 1e9, 4), "unit": "GB/s",
             "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(), "kind": "port",
             "seconds": round(t, 2),
-            "sample": f"first {n} of {w.num_seqs} sequences of the workload, CPU oracle "
+            "sample": f"first {n} of {w.num_seqs} sequences of the workload, {reps} passes, CPU oracle "
                       f"(torch fp32, {torch.get_num_threads()} threads)"}
 
 
@@ -509,9 +550,7 @@ def run_reference_arm(a, spec: dict, variant: str, world: int) -> None:
         "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(dt * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU)",
         "data": "synthetic",
-        "config": {"workload": f"BASELINE config {a.config[1]}: {variant} variant, KV {spec['kv']}, "
-                               f"num_seqs={spec['num_seqs']}, heads={spec['heads']}/{spec['kv_heads']}, "
-                               f"head_size=128, block_size=16, ctx={spec['ctx']}"},
+        "config": describe_config(a, spec, variant, world, ctx),
         "cpu_baseline": {"value": round(value, 4), "unit": "GB/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": desc},
         "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

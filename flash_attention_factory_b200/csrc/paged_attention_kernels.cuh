@@ -121,42 +121,79 @@ __device__ __forceinline__ uint32_t acc_dim_index(uint32_t tile, uint32_t h, uin
 // One unit of work of a CTA: tokens [tok_begin, tok_end) of KV heads
 // [head_base, head_base + hpc) of one sequence.
 struct WorkItem {
-  uint32_t linear; // position in the dense (seq, partition, head group) enumeration (split mode)
+  uint32_t linear; // item number (split mode), see SplitCursor
   uint32_t seq, head_base, partition;
   uint32_t tok_begin, tok_end;
   bool valid;
 };
 
-// Split mode: CTA b handles the items b, b + gridDim.x, ... of the dense enumeration with
-// the head group fastest (CTAs that run together stream neighbouring rows of the same KV
-// blocks); partitions that start at or past the context are skipped and their scratch rows
-// stay untouched (reference paged_attention_kernel_v2.hpp:194-200,577-579).
+// Split mode: the work items are the (sequence, partition, head group) triples whose partition
+// starts inside the context, numbered densely with the head group fastest (CTAs that run
+// together stream neighbouring rows of the same KV blocks) and the sequence slowest; CTA b
+// takes the items b, b + gridDim.x, ...  Partitions past a context have no number, so their
+// scratch rows stay untouched (reference paged_attention_kernel_v2.hpp:194-200,577-579) and
+// ragged batches spread evenly: every CTA gets the same count of items to within one.
+//
+// The numbering needs the running sum of items per sequence.  A warp keeps a window of 32
+// sequences in registers (one per lane) and moves it forward as its item numbers grow, so the
+// context lengths are read once per warp over the life of the kernel.  Every method is
+// called by all 32 lanes of a warp together.
 template <uint32_t PARTITION>
-__device__ __forceinline__ WorkItem find_split_item(uint32_t linear, const AttnArgs &args) {
-  WorkItem it{};
-  const uint32_t groups = args.num_kv_heads / args.hpc;
-  const uint32_t per_seq = groups * args.max_num_partitions;
-  const uint32_t total = per_seq * args.num_seqs;
-  it.valid = false;
-  while (linear < total) {
-    const uint32_t seq = linear / per_seq;
-    const uint32_t rem = linear - seq * per_seq;
-    const uint32_t part = rem / groups;
-    const uint32_t ctx = __ldg(args.context_lens + seq);
-    if (part * PARTITION < ctx) {
-      it.linear = linear;
-      it.seq = seq;
-      it.head_base = (rem - part * groups) * args.hpc;
-      it.partition = part;
-      it.tok_begin = part * PARTITION;
-      it.tok_end = min(ctx, it.tok_begin + PARTITION);
-      it.valid = true;
-      return it;
+struct SplitCursor {
+  uint32_t window_seq;     // first sequence of the window (multiple of 32)
+  uint32_t items_before;   // items of all sequences before the window
+  uint32_t lane_ctx;       // context length of sequence window_seq + lane (0 past the batch)
+  uint32_t lane_incl;      // items of sequences window_seq .. window_seq + lane (inclusive scan)
+  uint32_t window_items;   // items of the whole window
+
+  __device__ __forceinline__ void load_window(const AttnArgs &args, uint32_t groups, uint32_t lane) {
+    const uint32_t seq = window_seq + lane;
+    lane_ctx = (seq < args.num_seqs) ? __ldg(args.context_lens + seq) : 0u;
+    const uint32_t parts = min(divide_round_up(lane_ctx, PARTITION), args.max_num_partitions);
+    uint32_t v = parts * groups;
+#pragma unroll
+    for (uint32_t o = 1; o < 32; o <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += up;
     }
-    linear += gridDim.x;
+    lane_incl = v;
+    window_items = __shfl_sync(0xffffffffu, v, 31);
   }
-  return it;
-}
+
+  __device__ __forceinline__ void init(const AttnArgs &args, uint32_t groups, uint32_t lane) {
+    window_seq = 0;
+    items_before = 0;
+    load_window(args, groups, lane);
+  }
+
+  // Item number `index` (never smaller than the previous one asked for) -> work item.
+  __device__ __forceinline__ WorkItem seek(uint32_t index, const AttnArgs &args, uint32_t groups,
+                                           uint32_t lane) {
+    WorkItem it{};
+    it.valid = false;
+    while (index >= items_before + window_items) {
+      if (window_seq + 32 >= args.num_seqs) return it; // past the last item
+      items_before += window_items;
+      window_seq += 32;
+      load_window(args, groups, lane);
+    }
+    const uint32_t local = index - items_before;
+    // the owning sequence is the first lane whose inclusive count exceeds `local`
+    const uint32_t owner = __ffs(__ballot_sync(0xffffffffu, lane_incl > local)) - 1u;
+    const uint32_t incl = __shfl_sync(0xffffffffu, lane_incl, owner);
+    const uint32_t ctx = __shfl_sync(0xffffffffu, lane_ctx, owner);
+    const uint32_t parts = min(divide_round_up(ctx, PARTITION), args.max_num_partitions);
+    const uint32_t within = local - (incl - parts * groups); // item number inside the sequence
+    it.linear = index;
+    it.seq = window_seq + owner;
+    it.partition = within / groups;
+    it.head_base = (within - it.partition * groups) * args.hpc;
+    it.tok_begin = it.partition * PARTITION;
+    it.tok_end = min(ctx, it.tok_begin + PARTITION);
+    it.valid = true;
+    return it;
+  }
+};
 
 template <int D, int KV>
 __device__ __forceinline__ void load_q_fragments(uint32_t (&qf)[D / 16][2], const AttnArgs &args,
@@ -215,14 +252,18 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   const uint32_t hpc = args.hpc;
   const uint32_t tps = args.tokens_per_stage;
 
-  // ---- the first work item of this CTA (integer bookkeeping, bit-exact)
+  // ---- the first work item of this CTA (integer bookkeeping, bit-exact); every warp keeps
+  // its own cursor over the item numbering and walks it in step with its own loop
   uint32_t cta_rank = 0, num_ranks = 1;
   WorkItem first{};
+  SplitCursor<policy::partition_size> cursor{};
+  const uint32_t head_groups = args.num_kv_heads / hpc;
   if constexpr (MODE == MODE_SPLIT) {
     // let the merge kernel's CTAs be scheduled as this grid's CTAs retire (it waits for the
     // completion of this grid before it reads anything)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    first = find_split_item<policy::partition_size>(blockIdx.x, args);
+    cursor.init(args, head_groups, lane);
+    first = cursor.seek(blockIdx.x, args, head_groups, lane);
   } else {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
@@ -282,7 +323,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       WorkItem nxt{};
       nxt.valid = false;
       if constexpr (MODE == MODE_SPLIT)
-        nxt = find_split_item<policy::partition_size>(cur.linear + gridDim.x, args);
+        nxt = cursor.seek(cur.linear + gridDim.x, args, head_groups, lane);
       const uint32_t total_chunks = divide_round_up(cur.tok_end - cur.tok_begin, rows);
       const int32_t head_coord = static_cast<int32_t>(cur.head_base + lane_head);
       for (uint32_t chunk0 = 0; chunk0 < total_chunks && alive; chunk0 += chunks_per_batch) {
@@ -441,7 +482,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       WorkItem nxt{};
       nxt.valid = false;
       if constexpr (MODE == MODE_SPLIT)
-        nxt = find_split_item<policy::partition_size>(cur.linear + gridDim.x, args);
+        nxt = cursor.seek(cur.linear + gridDim.x, args, head_groups, lane);
       const uint32_t kv_head = cur.head_base + my_head;
 
       m_ref[0] = m_ref[1] = m_true[0] = m_true[1] = neg_infinity();
