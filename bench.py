@@ -257,8 +257,17 @@ def cpu_sample_inputs(w: Workload, n_seq: int):
                 sm_scale=w.sm_scale, fp8_scale=w.fp8_scale)
 
 
+def use_all_host_threads() -> None:
+    """torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core."""
+    n = os.cpu_count() or 1
+    if torch.get_num_threads() != n:
+        torch.set_num_threads(n)
+
+
 def time_cpu_oracle(sample: dict) -> float:
     from oracle import paged_attention_oracle as oracle
+
+    use_all_host_threads()
 
     t0 = time.perf_counter()
     oracle.paged_attention_ref(sample["query"], sample["key_cache"], sample["value_cache"],
