@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = (
     "launch_kernels_fp8_loop",
     "launch_kernels_fp8_reduce",
     "launch_kernels_reduce_static_scratch",
+    "pa_reshape_and_cache",
     "pa_query_policy",
     "pa_partition_size",
     "pa_last_error",
@@ -87,6 +88,25 @@ class PaPolicyInfo(ctypes.Structure):
     ]
 
 
+class PaCacheWriteParams(ctypes.Structure):
+    """struct pa_cache_write_params of include/paged_attention_b200.h."""
+
+    _fields_ = [
+        ("key", ctypes.c_void_p),
+        ("value", ctypes.c_void_p),
+        ("key_cache", ctypes.c_void_p),
+        ("value_cache", ctypes.c_void_p),
+        ("slot_mapping", ctypes.c_void_p),
+        ("num_tokens", ctypes.c_uint32),
+        ("num_kv_heads", ctypes.c_uint32),
+        ("head_size", ctypes.c_uint32),
+        ("block_size", ctypes.c_uint32),
+        ("num_blocks", ctypes.c_uint64),
+        ("fp8_scale", ctypes.c_float),
+        ("kv_dtype", ctypes.c_int32),
+    ]
+
+
 def library_path() -> Path:
     return Path(__file__).resolve().parent / _LIB_NAME
 
@@ -111,6 +131,8 @@ def load_library() -> ctypes.CDLL:
         fn.restype = ctypes.c_int
     lib.launch_kernels_reduce_static_scratch.argtypes = [ctypes.POINTER(PaParams), ctypes.c_void_p]
     lib.launch_kernels_reduce_static_scratch.restype = ctypes.c_int
+    lib.pa_reshape_and_cache.argtypes = [ctypes.POINTER(PaCacheWriteParams), ctypes.c_void_p]
+    lib.pa_reshape_and_cache.restype = ctypes.c_int
     lib.pa_query_policy.argtypes = [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
                                     ctypes.POINTER(PaPolicyInfo)]
     lib.pa_query_policy.restype = ctypes.c_int

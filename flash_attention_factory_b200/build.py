@@ -28,6 +28,7 @@ SOURCES = [
     "launch_kernels_reduce.cu",
     "launch_kernels_fp8_loop.cu",
     "launch_kernels_fp8_reduce.cu",
+    "cache_write.cu",
 ]
 
 NVCC_FLAGS = [

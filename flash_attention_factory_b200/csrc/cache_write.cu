@@ -1,0 +1,96 @@
+// pa_reshape_and_cache: appends new K/V tokens to the paged cache, quantising to FP8 on the way.
+//
+// The step that precedes the attention path in a decode loop.  The reference has no such
+// kernel: its tests build caches on the host with torch casts (test_paged_fp8cache.py:180-203)
+// in the layout the attention kernels read, [num_blocks, block_size, num_kv_heads, head_size]
+// (paged_attention_kernel_loop.hpp:50-51).  This kernel defines the same contract on the
+// device: value stored = round-to-nearest-even(x / fp8_scale) in e5m2 or e4m3 (saturating to
+// the largest finite code), or x itself for an fp16 cache.
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include "launch_common.cuh"
+
+namespace pa {
+
+// 8 fp16 values (one 16-byte load) -> 8 cache elements
+template <int KV>
+__device__ __forceinline__ void store_converted(void *dst_row, uint32_t elem, uint4 v, float scale) {
+  if constexpr (KV == KV_F16) {
+    *reinterpret_cast<uint4 *>(static_cast<__half *>(dst_row) + elem) = v;
+  } else {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+    uint32_t packed[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      // IEEE division in fp32, then one rounding to FP8: the arithmetic of
+      // (x.float() / scale).to(float8) for every value inside the format's range
+      const float2 a = __half22float2(h[2 * i]);
+      const float2 b = __half22float2(h[2 * i + 1]);
+      constexpr __nv_fp8_interpretation_t fmt = (KV == KV_E5M2) ? __NV_E5M2 : __NV_E4M3;
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(a.x, scale), __fdiv_rn(a.y, scale)),
+                                                   __NV_SATFINITE, fmt);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(b.x, scale), __fdiv_rn(b.y, scale)),
+                                                   __NV_SATFINITE, fmt);
+      packed[i] = lo | (hi << 16);
+    }
+    *reinterpret_cast<uint2 *>(static_cast<uint8_t *>(dst_row) + elem) = make_uint2(packed[0], packed[1]);
+  }
+}
+
+// One CTA per new token; a thread moves 8 elements of K and 8 of V per step.
+template <int KV>
+__global__ void __launch_bounds__(128)
+reshape_and_cache_kernel(const __half *__restrict__ key, const __half *__restrict__ value,
+                         void *__restrict__ key_cache, void *__restrict__ value_cache,
+                         const int64_t *__restrict__ slot_mapping, uint32_t row_elems, uint64_t num_slots,
+                         float scale) {
+  const uint32_t token = blockIdx.x;
+  const int64_t slot = slot_mapping[token];
+  if (slot < 0 || static_cast<uint64_t>(slot) >= num_slots) return; // padding token / out of range
+  constexpr uint32_t ELT = (KV == KV_F16) ? 2u : 1u;
+  const __half *ksrc = key + static_cast<size_t>(token) * row_elems;
+  const __half *vsrc = value + static_cast<size_t>(token) * row_elems;
+  uint8_t *kdst = static_cast<uint8_t *>(key_cache) + static_cast<size_t>(slot) * row_elems * ELT;
+  uint8_t *vdst = static_cast<uint8_t *>(value_cache) + static_cast<size_t>(slot) * row_elems * ELT;
+  for (uint32_t e = threadIdx.x * 8; e < row_elems; e += blockDim.x * 8) {
+    const uint4 kv = __ldg(reinterpret_cast<const uint4 *>(ksrc + e));
+    const uint4 vv = __ldg(reinterpret_cast<const uint4 *>(vsrc + e));
+    store_converted<KV>(kdst, e, kv, scale);
+    store_converted<KV>(vdst, e, vv, scale);
+  }
+}
+
+} // namespace pa
+
+extern "C" PA_API int pa_reshape_and_cache(const pa_cache_write_params *p, void *stream) {
+  using namespace pa;
+  if (p == nullptr) return fail(PA_ERR_BAD_ARG, "params is null");
+  if (p->kv_dtype != PA_KV_F16 && p->kv_dtype != PA_KV_FP8_E5M2 && p->kv_dtype != PA_KV_FP8_E4M3)
+    return fail(PA_ERR_BAD_ARG, "unknown kv_dtype %d", p->kv_dtype);
+  if (p->num_tokens == 0) return PA_OK;
+  if (!p->key || !p->value || !p->key_cache || !p->value_cache || !p->slot_mapping)
+    return fail(PA_ERR_BAD_ARG, "a required pointer is null");
+  const uint64_t row_elems = static_cast<uint64_t>(p->num_kv_heads) * p->head_size;
+  if (row_elems == 0 || row_elems % 8 != 0 || row_elems > (1u << 20))
+    return fail(PA_ERR_BAD_ARG, "num_kv_heads * head_size must be a positive multiple of 8");
+  if (p->block_size == 0 || p->num_blocks == 0) return fail(PA_ERR_BAD_ARG, "empty cache");
+  if (p->kv_dtype != PA_KV_F16 && !(p->fp8_scale > 0.f))
+    return fail(PA_ERR_BAD_ARG, "fp8_scale must be positive and finite");
+  if (!aligned16(p->key) || !aligned16(p->value) || !aligned16(p->key_cache) || !aligned16(p->value_cache))
+    return fail(PA_ERR_BAD_ARG, "key / value / caches must be 16-byte aligned");
+  const uint64_t num_slots = p->num_blocks * p->block_size;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(p->num_tokens), block(128);
+  const uint32_t re = static_cast<uint32_t>(row_elems);
+  const __half *k = static_cast<const __half *>(p->key);
+  const __half *v = static_cast<const __half *>(p->value);
+  if (p->kv_dtype == PA_KV_F16)
+    reshape_and_cache_kernel<KV_F16><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, 1.f);
+  else if (p->kv_dtype == PA_KV_FP8_E5M2)
+    reshape_and_cache_kernel<KV_E5M2><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, p->fp8_scale);
+  else
+    reshape_and_cache_kernel<KV_E4M3><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, p->fp8_scale);
+  PA_CUDA_TRY(cudaGetLastError());
+  return PA_OK;
+}

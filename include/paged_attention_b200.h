@@ -167,6 +167,30 @@ PA_API int launch_kernels_fp8_reduce(const pa_params *p, void *stream, float *us
  * array needs clearing between calls. */
 PA_API int launch_kernels_reduce_static_scratch(const pa_params *p, void *stream);
 
+/* Arguments of pa_reshape_and_cache. */
+typedef struct pa_cache_write_params {
+  const void *key;             /* fp16 [num_tokens, num_kv_heads, head_size] */
+  const void *value;           /* fp16 [num_tokens, num_kv_heads, head_size] */
+  void *key_cache;             /* [num_blocks, block_size, num_kv_heads, head_size], fp16 or FP8 */
+  void *value_cache;           /* same layout and type as key_cache */
+  const int64_t *slot_mapping; /* [num_tokens]: block_id * block_size + row; negative = skip the token */
+  uint32_t num_tokens;
+  uint32_t num_kv_heads;
+  uint32_t head_size;
+  uint32_t block_size;
+  uint64_t num_blocks;
+  float fp8_scale;             /* stored = x / fp8_scale (the scale the attention entry points take) */
+  int32_t kv_dtype;            /* pa_kv_dtype of the cache */
+} pa_cache_write_params;
+
+/* Appends new K/V tokens to the paged cache in the layout the attention entry points read
+ * (reference paged_attention_kernel_loop.hpp:50-51), casting to the cache type: fp16 is
+ * copied, FP8 is round-to-nearest-even of x / fp8_scale, saturating to the largest finite
+ * code.  The reference has no device kernel for this step: its tests fill caches on the host
+ * with torch casts (test_paged_fp8cache.py:180-203), which this call reproduces bit for bit for
+ * values inside the format's range.  Asynchronous on `stream`. */
+PA_API int pa_reshape_and_cache(const pa_cache_write_params *p, void *stream);
+
 /* Compile-time policy of include/paged_attention_policy_v2.hpp as data
  * (reference include/paged_attention_policy_v2.hpp:5-100).  Returns
  * PA_ERR_UNSUPPORTED for triples the launchers reject. */

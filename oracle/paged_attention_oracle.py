@@ -174,3 +174,28 @@ def merge_partitions_ref(max_logits, exp_sums, tmp_out, context_lens, partition_
 def kv_bytes(context_lens: Sequence[int], num_kv_heads: int, head_size: int, elt_bytes: int) -> int:
     """Algorithmic HBM bytes of one call: every cached K and V element once."""
     return int(sum(int(c) for c in context_lens)) * num_kv_heads * head_size * 2 * elt_bytes
+
+
+def reshape_and_cache_ref(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor,
+                          value_cache: torch.Tensor, slot_mapping: torch.Tensor, fp8_scale: float = 1.0):
+    """CPU statement of the cache append: returns new (key_cache, value_cache).
+
+    Token t goes to flat slot slot_mapping[t] = block_id * block_size + row of the
+    [num_blocks, block_size, kv_heads, head_size] cache (layout of
+    paged_attention_loop/paged_attention_kernel_loop.hpp:50-51); negative slots are skipped.
+    The cast is the reference fixture's: `x.to(fp8_dtype)` on the fp16 data
+    (test_paged_fp8cache.py:201-203), after dividing by the per-tensor scale in fp32.
+    """
+    kc, vc = key_cache.clone(), value_cache.clone()
+    dt = kc.dtype
+    flat_k = kc.view(-1, *kc.shape[2:])
+    flat_v = vc.view(-1, *vc.shape[2:])
+    for t, slot in enumerate(slot_mapping.tolist()):
+        if slot < 0 or slot >= flat_k.shape[0]:
+            continue
+        if dt == torch.float16:
+            flat_k[slot], flat_v[slot] = key[t], value[t]
+        else:
+            flat_k[slot] = (key[t].float() / fp8_scale).to(dt)
+            flat_v[slot] = (value[t].float() / fp8_scale).to(dt)
+    return kc, vc

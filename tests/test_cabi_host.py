@@ -151,3 +151,23 @@ def test_no_cpu_fallback():
             torch.zeros(s, h, d), torch.zeros(s, h, d).half(), torch.zeros(1, 16, 1, d).half(),
             torch.zeros(1, 16, 1, d).half(), torch.zeros(s, 1, dtype=torch.int32),
             torch.ones(s, dtype=torch.int32), 2, 0.1, 16, 1, torch.ones(h), None, -1.0)
+
+
+def test_cache_write_validates_on_the_host(lib):
+    def call(**kw):
+        p = _cabi.PaCacheWriteParams()
+        base = dict(key=0x1000, value=0x2000, key_cache=0x3000, value_cache=0x4000, slot_mapping=0x5000,
+                    num_tokens=3, num_kv_heads=2, head_size=128, block_size=16, num_blocks=4,
+                    fp8_scale=1.0, kv_dtype=_cabi.KV_FP8_E4M3)
+        base.update(kw)
+        for k, v in base.items():
+            setattr(p, k, v)
+        return lib.pa_reshape_and_cache(ctypes.byref(p), None), lib.pa_last_error().decode()
+
+    assert call(num_tokens=0)[0] == _cabi.PA_OK
+    assert call(kv_dtype=7)[0] == _cabi.PA_ERR_BAD_ARG
+    assert call(key=0)[0] == _cabi.PA_ERR_BAD_ARG
+    assert call(head_size=3)[0] == _cabi.PA_ERR_BAD_ARG
+    assert call(fp8_scale=0.0)[0] == _cabi.PA_ERR_BAD_ARG
+    assert call(key_cache=0x3004)[0] == _cabi.PA_ERR_BAD_ARG
+    assert lib.pa_reshape_and_cache(None, None) == _cabi.PA_ERR_BAD_ARG

@@ -1,0 +1,75 @@
+"""pa_reshape_and_cache: bit-exact against the CPU statement of the reference's fixture casts."""
+import pytest
+import torch
+
+from _util import FP8_DTYPES, assert_close, make_case, run_entry
+from oracle import paged_attention_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(t):
+    return t.view(torch.int16) if t.dtype == torch.float16 else t.view(torch.uint8)
+
+
+@pytest.mark.parametrize("kv,scale", [("float16", 1.0), ("float8_e5m2", 1.0), ("float8_e4m3fn", 1.0),
+                                      ("float8_e4m3fn", 0.0123), ("float8_e5m2", 3.0)])
+@pytest.mark.parametrize("hk,d,bs", [(8, 128, 16), (2, 64, 64), (1, 128, 32)])
+def test_append_is_bit_exact(cuda_device, kv, scale, hk, d, bs):
+    from flash_attention_factory_b200.cache_ops import reshape_and_cache
+
+    g = torch.Generator().manual_seed(hk * 1000 + d + bs)
+    nb, t = 12, 37
+    dt = torch.float16 if kv == "float16" else FP8_DTYPES[kv]
+    # values stay inside the format's range after scaling: |x / scale| < 448 for e4m3
+    key = (torch.randn(t, hk, d, generator=g) * (scale if scale != 1.0 else 1.0) * 20).to(torch.float16)
+    value = (torch.randn(t, hk, d, generator=g) * (scale if scale != 1.0 else 1.0) * 20).to(torch.float16)
+    kc = torch.randn(nb, bs, hk, d, generator=g).to(torch.float16).to(dt)
+    vc = torch.randn(nb, bs, hk, d, generator=g).to(torch.float16).to(dt)
+    slots = torch.randperm(nb * bs, generator=g)[:t].to(torch.int64)
+    slots[5] = -1  # padding token: skipped
+    want_k, want_v = oracle.reshape_and_cache_ref(key, value, kc, vc, slots, scale)
+    dk, dv = kc.to(cuda_device), vc.to(cuda_device)
+    reshape_and_cache(key.to(cuda_device), value.to(cuda_device), dk, dv, slots.to(cuda_device), scale)
+    torch.cuda.synchronize(cuda_device)
+    assert torch.equal(_bits(dk.cpu()), _bits(want_k))
+    assert torch.equal(_bits(dv.cpu()), _bits(want_v))
+
+
+def test_fp8_overflow_saturates(cuda_device):
+    from flash_attention_factory_b200.cache_ops import reshape_and_cache
+
+    key = torch.full((1, 1, 8), 1000.0, dtype=torch.float16)
+    key[0, 0, 1] = -60000.0
+    kc = torch.zeros(1, 16, 1, 8, dtype=torch.float8_e4m3fn, device=cuda_device)
+    vc = torch.zeros_like(kc)
+    reshape_and_cache(key.to(cuda_device), key.to(cuda_device), kc, vc,
+                      torch.zeros(1, dtype=torch.int64, device=cuda_device), 1.0)
+    got = kc[0, 0, 0].float().cpu()
+    assert got[0] == 448.0 and got[1] == -448.0  # largest finite e4m3 code, not NaN
+
+
+@pytest.mark.parametrize("kv", ["float8_e5m2", "float8_e4m3fn"])
+def test_decode_step_append_then_attend(cuda_device, kv):
+    """One decode step end to end: the kernel appends token ctx of every sequence, attention
+    over ctx + 1 tokens then equals the oracle on a cache built with torch casts."""
+    from flash_attention_factory_b200.cache_ops import reshape_and_cache
+
+    ctx = [100, 511, 512, 37]
+    c = make_case(seed=77, num_seqs=4, num_heads=8, num_kv_heads=2, head_size=128, block_size=16,
+                  context_lens=[n + 1 for n in ctx], kv_dtype=kv, fp8_scale=0.05)
+    g = torch.Generator().manual_seed(3)
+    new_k = (torch.randn(4, 2, 128, generator=g)).to(torch.float16)
+    new_v = (torch.randn(4, 2, 128, generator=g)).to(torch.float16)
+    slots = torch.tensor([int(c["block_tables"][i, n // 16]) * 16 + n % 16 for i, n in enumerate(ctx)])
+    want_k, want_v = oracle.reshape_and_cache_ref(new_k, new_v, c["key_cache"], c["value_cache"], slots,
+                                                  c["fp8_scale"])
+    dk, dv = c["key_cache"].to(cuda_device), c["value_cache"].to(cuda_device)
+    reshape_and_cache(new_k.to(cuda_device), new_v.to(cuda_device), dk, dv, slots.to(cuda_device),
+                      c["fp8_scale"])
+    c2 = dict(c)
+    c2["key_cache"], c2["value_cache"] = dk.cpu(), dv.cpu()
+    want = oracle.paged_attention_ref(c["query"], want_k, want_v, c["block_tables"], c["context_lens"],
+                                      sm_scale=c["sm_scale"], fp8_scale=c["fp8_scale"])
+    for variant in ("loop", "reduce"):
+        assert_close(run_entry(variant, c2, cuda_device)["out"], want, what=f"append+attend/{kv}/{variant}")
