@@ -297,6 +297,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       tma_prefetch_descriptor(&tmap_k);
       tma_prefetch_descriptor(&tmap_v);
     }
+    const uint64_t kv_policy = l2_evict_first_policy(); // every KV byte is read once
     const uint32_t rows = args.rows_per_box;
     const uint32_t bps = args.boxes_per_stage;
     const uint32_t chunks_per_stage = bps / hpc;      // token chunks (boxes per head) in a stage
@@ -357,8 +358,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
             for (uint32_t sl = 0; sl < geo::num_slabs; ++sl) {
               const uint32_t dst = stage_base + sl * L::SLAB_TILE + row0 * geo::slab_bytes;
               const int32_t x = static_cast<int32_t>(sl * geo::slab_elems);
-              tma_load_3d(dst, &tmap_k, &full_bar[slot], x, y, head_coord);
-              tma_load_3d(dst + L::KV_TILE, &tmap_v, &full_bar[slot], x, y, head_coord);
+              tma_load_3d(dst, &tmap_k, &full_bar[slot], x, y, head_coord, kv_policy);
+              tma_load_3d(dst + L::KV_TILE, &tmap_v, &full_bar[slot], x, y, head_coord, kv_policy);
             }
           }
           if (++slot == NSTAGES) {

@@ -215,13 +215,21 @@ PA_DEV void tma_load_2d(uint32_t dst_smem, const void *tensor_map, uint64_t *bar
       "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// L2 policy for data that is read exactly once (the KV stream): evict it first
+PA_DEV uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+
 // Tiled 3-D copy global -> this CTA's shared memory, completion on `bar`.
 PA_DEV void tma_load_3d(uint32_t dst_smem, const void *tensor_map, uint64_t *bar, int32_t x,
-                        int32_t y, int32_t z) {
+                        int32_t y, int32_t z, uint64_t l2_policy) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst_smem),
-      "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(dst_smem),
+      "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z),
+      "l"(l2_policy)
       : "memory");
 }
 PA_DEV void tma_prefetch_descriptor(const void *tensor_map) {
