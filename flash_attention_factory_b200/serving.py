@@ -37,7 +37,7 @@ class AutoDecodePlan:
     into loop / reduce sequences stays the same (rebuild it when sequences join or leave)."""
 
     def __init__(self, context_lens_host: Sequence[int], num_heads: int, head_size: int, block_size: int,
-                 max_blocks_per_seq: int, device, split_threshold_partitions: int = 4):
+                 max_blocks_per_seq: int, device, split_threshold_partitions: int = 2):
         self.device = torch.device(device)
         self.psize = _cabi.partition_size(head_size)
         self.block_size = block_size
