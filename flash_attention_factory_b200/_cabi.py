@@ -68,6 +68,8 @@ class PaParams(ctypes.Structure):
         ("fp8_scale", ctypes.c_float),
         ("kv_dtype", ctypes.c_int32),
         ("reserved1", ctypes.c_int32),
+        ("k_scale_per_head", ctypes.c_void_p),
+        ("v_scale_per_head", ctypes.c_void_p),
     ]
 
 

@@ -92,6 +92,8 @@ inline int validate_params(const pa_params *p, bool fp8_entry, bool needs_scratc
   }
   if (!(p->sm_scale > 0.f) || (fp8_entry && !(p->fp8_scale > 0.f)))
     return fail(PA_ERR_BAD_ARG, "sm_scale and fp8_scale must be positive and finite");
+  if (!fp8_entry && (p->k_scale_per_head != nullptr || p->v_scale_per_head != nullptr))
+    return fail(PA_ERR_BAD_ARG, "per-head scales belong to the FP8 entry points");
   if (p->num_seqs == 0) return PA_OK; // nothing to do; the launcher returns early
   if (!p->out || !p->query || !p->key_cache || !p->value_cache || !p->block_tables || !p->context_lens)
     return fail(PA_ERR_BAD_ARG, "a required pointer is null");
@@ -187,6 +189,9 @@ AttnArgs make_attn_args(const pa_params *p) {
   // (reference paged_attention_kernel_fp8_loop.hpp:333,545)
   a.scale_log2 = p->sm_scale * kv_scale * kLog2e;
   a.out_scale = kv_scale;
+  a.sm_scale_log2 = p->sm_scale * kLog2e;
+  a.k_scale_per_head = (KV == KV_F16) ? nullptr : p->k_scale_per_head;
+  a.v_scale_per_head = (KV == KV_F16) ? nullptr : p->v_scale_per_head;
   return a;
 }
 
@@ -254,6 +259,23 @@ int enqueue_merge(const pa_params *p, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  // Many (sequence, head) pairs: a warp per pair keeps more rows in flight than a CTA per pair.
+  // Both kernels add in the same order and give the same bits (tested), so the choice is free.
+  // Debugging knob: PA_MERGE_KERNEL=cta|warp forces one of them.
+  static const int forced = [] {
+    const char *e = std::getenv("PA_MERGE_KERNEL");
+    return e == nullptr ? 0 : (e[0] == 'c' ? 1 : (e[0] == 'w' ? 2 : 0));
+  }();
+  const uint64_t pairs = static_cast<uint64_t>(p->num_seqs) * p->num_heads;
+  if (forced == 2 || (forced == 0 && pairs >= 8192)) {
+    cfg.gridDim = dim3(static_cast<unsigned>((pairs + 3) / 4), 1, 1);
+    PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partitions_warp_kernel<D>, static_cast<__half *>(p->out),
+                                   static_cast<const __half *>(p->tmp_out),
+                                   static_cast<const float *>(p->max_logits),
+                                   static_cast<const float *>(p->exp_sums), p->context_lens, p->num_heads,
+                                   static_cast<uint32_t>(pairs), p->max_num_partitions, psize));
+    return PA_OK;
+  }
   PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partitions_kernel<D>, static_cast<__half *>(p->out),
                                  static_cast<const __half *>(p->tmp_out),
                                  static_cast<const float *>(p->max_logits),

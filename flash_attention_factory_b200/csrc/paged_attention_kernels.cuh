@@ -70,6 +70,11 @@ struct AttnArgs {
   uint32_t heads_per_box;    // KV heads one TMA box covers: hpc if rows_per_box == tokens_per_stage, else 1
   float scale_log2;          // sm_scale * fp8_scale * log2(e), > 0
   float out_scale;           // fp8_scale (1 for fp16)
+  // optional per-KV-head dequantisation scales of an FP8 cache, [num_kv_heads] each; when
+  // set they take the place of fp8_scale for K and for V
+  const float *k_scale_per_head;
+  const float *v_scale_per_head;
+  float sm_scale_log2;       // sm_scale * log2(e)
 };
 
 constexpr float kLn2 = 0.6931471805599453f;
@@ -377,7 +382,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t t4 = lane & 3u;
     const uint32_t G = args.group;
     const uint32_t ctid = threadIdx.x - 32; // 0 .. NCONS-1
-    const float scale = args.scale_log2;
     // warp -> (head inside the group, 16-token slice inside the stage)
     const uint32_t slices = NW / hpc; // token slices per head: 4, 2 or 1
     const uint32_t my_head = cw / slices;
@@ -485,6 +489,12 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       if constexpr (MODE == MODE_SPLIT)
         nxt = cursor.seek(cur.linear + gridDim.x, args, head_groups, lane);
       const uint32_t kv_head = cur.head_base + my_head;
+      // softmax scale (log2 domain) and output scale of this warp's KV head
+      const float scale = (args.k_scale_per_head != nullptr)
+                              ? args.sm_scale_log2 * __ldg(args.k_scale_per_head + kv_head)
+                              : args.scale_log2;
+      const float out_scale = (args.v_scale_per_head != nullptr) ? __ldg(args.v_scale_per_head + kv_head)
+                                                                 : args.out_scale;
 
       m_ref[0] = m_ref[1] = m_true[0] = m_true[1] = neg_infinity();
       l_run[0] = l_run[1] = 0.f; // per-lane partial sums; reduced over gid at the end
@@ -628,7 +638,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
               // report the true maximum; the sum is re-expressed relative to it
               const float l_true = l_run[j] * fast_exp2(m_ref[j] - m_true[j]);
               // normalised inside the partition (reference paged_attention_kernel_v2.hpp:386)
-              const float inv = (l_run[j] > 0.f) ? (args.out_scale / l_run[j]) : 0.f;
+              const float inv = (l_run[j] > 0.f) ? (out_scale / l_run[j]) : 0.f;
               __half *dst = args.tmp_out + pidx * D;
               if constexpr (KV == KV_F16) {
 #pragma unroll
@@ -735,7 +745,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
             if (g < G && ok) {
               const size_t head = static_cast<size_t>(cur.seq) * args.num_heads + (cur.head_base + hh) * G + g;
               const size_t pidx = head * args.max_num_partitions + cur.partition;
-              const float inv = (l_all > 0.f) ? (args.out_scale / l_all) : 0.f;
+              const float head_scale = (args.v_scale_per_head != nullptr)
+                                           ? __ldg(args.v_scale_per_head + cur.head_base + hh)
+                                           : args.out_scale;
+              const float inv = (l_all > 0.f) ? (head_scale / l_all) : 0.f;
               uint4 packed;
               packed.x = pack_half2(lo.x * inv, lo.y * inv);
               packed.y = pack_half2(lo.z * inv, lo.w * inv);
@@ -814,7 +827,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           // an empty context (l = 0) gives zeros
           const float inv = (l_all > 0.f) ? (1.f / l_all) : 0.f;
           const size_t head = static_cast<size_t>(first.seq) * args.num_heads + (first.head_base + hh) * G + g;
-          args.out[head * D + d] = __float2half_rn(o_all * args.out_scale * inv);
+          const float head_scale = (args.v_scale_per_head != nullptr)
+                                       ? __ldg(args.v_scale_per_head + first.head_base + hh)
+                                       : args.out_scale;
+          args.out[head * D + d] = __float2half_rn(o_all * head_scale * inv);
         }
       }
     }
@@ -931,6 +947,87 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
 #pragma unroll
     for (uint32_t r = 0; r < ROWS; ++r) s += part[r][tid];
     orow[tid] = __float2half_rn(s);
+  }
+}
+
+// Variant of merge_partitions_kernel for batches with many (sequence, head) pairs: one WARP
+// per pair (four pairs per CTA), no shared memory and no block barrier.  Each lane owns
+// D / 32 dims of the row.  Every sum is taken in the order merge_partitions_kernel uses
+// (weights: four 32-wide shuffle trees added left to right; rows: one accumulator per
+// residue class p mod ROWS, classes added in increasing order), so both kernels produce the
+// same bits and the launcher may pick either.
+template <int D>
+__global__ void __launch_bounds__(128)
+merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict__ tmp_out,
+                             const float *__restrict__ max_logits, const float *__restrict__ exp_sums,
+                             const uint32_t *__restrict__ context_lens, uint32_t num_heads,
+                             uint32_t num_pairs, uint32_t max_num_partitions, uint32_t partition_size) {
+  constexpr uint32_t DPL = D / 32;          // dims per lane: 4 or 2
+  constexpr uint32_t ROWS = 128 / (D / 4);  // residue classes of the CTA-per-pair kernel
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t pair = blockIdx.x * 4 + (threadIdx.x >> 5); // seq * num_heads + head
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (pair >= num_pairs) return;
+  const uint32_t seq = pair / num_heads;
+  const uint32_t ctx = context_lens[seq];
+  const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
+  const size_t base = static_cast<size_t>(pair) * max_num_partitions;
+  const __half *rows = tmp_out + base * D + lane * DPL;
+
+  float m = neg_infinity();
+  for (uint32_t p = lane; p < np; p += 32) m = fmaxf(m, max_logits[base + p]);
+#pragma unroll
+  for (uint32_t o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  // total weight: chunk c plays warp c of the CTA-per-pair kernel (threads 32c .. 32c+31)
+  float wsum = 0.f;
+#pragma unroll
+  for (uint32_t c = 0; c < 4; ++c) {
+    float part = 0.f;
+    for (uint32_t p = 32 * c + lane; p < np; p += 128) part += exp_sums[base + p] * __expf(max_logits[base + p] - m);
+#pragma unroll
+    for (uint32_t o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    wsum = (c == 0) ? part : wsum + part;
+  }
+  const float inv_w = (wsum > 0.f) ? 1.f / wsum : 0.f;
+
+  float acc[ROWS][DPL];
+#pragma unroll
+  for (uint32_t r = 0; r < ROWS; ++r)
+#pragma unroll
+    for (uint32_t i = 0; i < DPL; ++i) acc[r][i] = 0.f;
+  for (uint32_t p0 = 0; p0 < np; p0 += ROWS) {
+#pragma unroll
+    for (uint32_t r = 0; r < ROWS; ++r) {
+      const uint32_t p = p0 + r;
+      if (p < np) {
+        const float w = exp_sums[base + p] * __expf(max_logits[base + p] - m) * inv_w;
+        uint2 raw = make_uint2(0u, 0u);
+        if constexpr (DPL == 4) raw = __ldg(reinterpret_cast<const uint2 *>(rows + static_cast<size_t>(p) * D));
+        else raw.x = __ldg(reinterpret_cast<const uint32_t *>(rows + static_cast<size_t>(p) * D));
+        const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+        acc[r][0] += w * v01.x;
+        acc[r][1] += w * v01.y;
+        if constexpr (DPL == 4) {
+          const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+          acc[r][2] += w * v23.x;
+          acc[r][3] += w * v23.y;
+        }
+      }
+    }
+  }
+  float total[DPL];
+#pragma unroll
+  for (uint32_t i = 0; i < DPL; ++i) {
+    float s = 0.f;
+#pragma unroll
+    for (uint32_t r = 0; r < ROWS; ++r) s += acc[r][i];
+    total[i] = s;
+  }
+  __half *orow = out + static_cast<size_t>(pair) * D + lane * DPL;
+  if constexpr (DPL == 4) {
+    *reinterpret_cast<uint2 *>(orow) = make_uint2(pack_half2(total[0], total[1]), pack_half2(total[2], total[3]));
+  } else {
+    *reinterpret_cast<uint32_t *>(orow) = pack_half2(total[0], total[1]);
   }
 }
 

@@ -34,7 +34,7 @@ def _kv_dtype_of(cache: torch.Tensor, fp8: bool) -> int:
 def build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
                  value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
                  fp8_scale, block_size, max_context_len, alibi_slopes, sinks, softcap,
-                 fp8: bool) -> _cabi.PaParams:
+                 fp8: bool, k_scale_per_head=None, v_scale_per_head=None) -> _cabi.PaParams:
     """Validates what the reference's ``data_ptr<float>()`` calls would and fills pa_params.
 
     ``debug_output``, ``alibi_slopes``, ``softcap`` are accepted and ignored like in the
@@ -89,6 +89,12 @@ def build_params(max_logits, exp_sums, tem_output, output, debug_output, query, 
     p.sm_scale = float(sm_scale)
     p.fp8_scale = float(fp8_scale)
     p.kv_dtype = _kv_dtype_of(key_cache, fp8)
+    for name, t in (("k_scale_per_head", k_scale_per_head), ("v_scale_per_head", v_scale_per_head)):
+        if t is not None:
+            _require(fp8, "per-head scales belong to the FP8 operators")
+            _require(t.dtype == torch.float32 and t.is_contiguous() and t.device == query.device
+                     and t.numel() == key_cache.size(2), f"{name} must be float32 [num_kv_heads] on the device")
+            setattr(p, name, t.data_ptr())
     return p
 
 

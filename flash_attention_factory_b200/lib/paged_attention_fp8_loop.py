@@ -25,10 +25,13 @@ def run(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache
 
 def enqueue(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
             block_tables, context_lens, num_queries_per_tokens, sm_scale, fp8_scale, block_size,
-            max_context_len, alibi_slopes, sinks, softcap):
-    """Same arguments as ``run`` but asynchronous on the current stream (returns nothing)."""
+            max_context_len, alibi_slopes, sinks, softcap, *, k_scale_per_head=None, v_scale_per_head=None):
+    """Same arguments as ``run`` but asynchronous on the current stream (returns nothing).
+
+    ``k_scale_per_head`` / ``v_scale_per_head`` (float32 [num_kv_heads], optional, no reference
+    counterpart) replace the scalar ``fp8_scale`` for K / V with one scale per KV head."""
     p = _shim.build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
                            value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
                            fp8_scale, block_size, max_context_len, alibi_slopes, sinks, softcap,
-                           fp8=True)
+                           fp8=True, k_scale_per_head=k_scale_per_head, v_scale_per_head=v_scale_per_head)
     _shim.enqueue_entry(_ENTRY, p, query.device)

@@ -87,6 +87,13 @@ typedef struct pa_params {
   float fp8_scale; /* per-tensor dequantisation scale of an FP8 cache; ignored for fp16 */
   int32_t kv_dtype; /* pa_kv_dtype; must match the entry point (fp16 vs FP8) */
   int32_t reserved1;
+  /* Optional per-KV-head dequantisation scales of an FP8 cache (device pointers, fp32
+   * [num_kv_heads] each, or NULL).  The reference has one scalar fp8_scale
+   * (paged_attention_fp8_loop/paged_attention_fp8_loop.cpp:34); when these are set,
+   * K of head k dequantises as fp16(code) * k_scale_per_head[k] and V as
+   * fp16(code) * v_scale_per_head[k], and fp8_scale is not used for that cache. */
+  const float *k_scale_per_head;
+  const float *v_scale_per_head;
 } pa_params;
 
 /* Tiling knobs of include/paged_attention_policy_v2.hpp for one

@@ -34,7 +34,10 @@ def dequantize_cache(cache: torch.Tensor, fp8_scale: float = 1.0) -> torch.Tenso
     if cache.dtype == torch.uint8:  # raw bytes mean e5m2, as in the reference binding
         cache = cache.view(torch.float8_e5m2)
     x = cache.to(torch.float16).to(torch.float32)
-    if fp8_scale != 1.0:
+    if torch.is_tensor(fp8_scale):
+        # one scale per KV head (an extension over the reference's scalar): [..., kv_heads, head_size]
+        x = x * fp8_scale.to(torch.float32).view(-1, 1)
+    elif fp8_scale != 1.0:
         x = x * fp8_scale
     return x
 
@@ -85,8 +88,11 @@ def attention_one_sequence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
 def paged_attention_ref(query: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
                         block_tables: torch.Tensor, context_lens: Sequence[int],
                         sm_scale: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
-                        fp8_scale: float = 1.0) -> torch.Tensor:
+                        fp8_scale: float = 1.0, k_scales: Optional[torch.Tensor] = None,
+                        v_scales: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Reference result of all four entry points: fp16 [num_seqs, num_heads, head_size].
+
+    `k_scales` / `v_scales` ([kv_heads] each) replace `fp8_scale` for K / V when given.
 
     query fp16 [S, H, D]; caches [num_blocks, block_size, HK, D] in fp16, float8_e5m2,
     float8_e4m3fn or uint8 (= e5m2).  One sequence at a time, which bounds memory the way
@@ -96,8 +102,10 @@ def paged_attention_ref(query: torch.Tensor, key_cache: torch.Tensor, value_cach
     out = torch.zeros(s, h, d, dtype=torch.float16)
     lens = [int(c) for c in context_lens]
     for i in range(s):
-        k = dequantize_cache(gather_sequence(key_cache, block_tables[i], lens[i]), fp8_scale)
-        v = dequantize_cache(gather_sequence(value_cache, block_tables[i], lens[i]), fp8_scale)
+        k = dequantize_cache(gather_sequence(key_cache, block_tables[i], lens[i]),
+                             fp8_scale if k_scales is None else k_scales)
+        v = dequantize_cache(gather_sequence(value_cache, block_tables[i], lens[i]),
+                             fp8_scale if v_scales is None else v_scales)
         o = attention_one_sequence(query[i].to(torch.float32), k, v, sinks, sm_scale)
         out[i] = o.to(torch.float16)  # test_paged.py:168
     return out

@@ -119,3 +119,44 @@ def test_out_of_range_block_ids_read_zeros_without_faulting(cuda_device):
     import flash_attention_factory_b200 as pkg
 
     pkg.device_status()
+
+
+@pytest.mark.parametrize("d,kv", [(128, "float16"), (64, "float8_e5m2")])
+def test_both_merge_kernels_give_the_same_bits(cuda_device, d, kv):
+    """The launcher picks the warp-per-head merge for large batches and the CTA-per-head one
+    otherwise; a sequence must not change its bits with the size of the batch it sits in."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+
+    # the kernel choice is read once per process: compare two child processes
+    code = textwrap.dedent(f"""
+        import sys, torch
+        sys.path.insert(0, {str(__import__('pathlib').Path(__file__).resolve().parent)!r})
+        from _util import make_case, run_entry
+        ctx = [3000, 513, 140 * {512 if d == 128 else 256}, 1, 7000, 2049]
+        c = make_case(seed=91, num_seqs=len(ctx), num_heads=8, num_kv_heads=2, head_size={d}, block_size=16,
+                      context_lens=ctx, kv_dtype={kv!r}, sinks=True)
+        out = run_entry("reduce", c, torch.device("cuda:0"))["out"]
+        torch.save(out, sys.argv[1])
+    """)
+    outs = []
+    for which in ("cta", "warp"):
+        path = f"/tmp/merge_{which}_{d}.pt"
+        env = dict(os.environ, PA_MERGE_KERNEL=which)
+        subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=600)
+        outs.append(torch.load(path))
+    assert torch.isfinite(outs[0].float()).all()
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_large_batch_takes_the_warp_merge_and_matches_the_oracle(cuda_device):
+    from _util import assert_close
+
+    ctx = [600 + 37 * (i % 40) for i in range(1024)]  # 1024 x 8 heads = 8192 (sequence, head) pairs
+    c = make_case(seed=92, num_seqs=1024, num_heads=8, num_kv_heads=8, head_size=64, block_size=64,
+                  context_lens=ctx, kv_dtype="float8_e5m2")
+    want = oracle.paged_attention_ref(c["query"], c["key_cache"], c["value_cache"], c["block_tables"],
+                                      c["context_lens"], sm_scale=c["sm_scale"])
+    assert_close(run_entry("reduce", c, cuda_device)["out"], want, what="large batch")
