@@ -70,6 +70,9 @@ class PaParams(ctypes.Structure):
         ("reserved1", ctypes.c_int32),
         ("k_scale_per_head", ctypes.c_void_p),
         ("v_scale_per_head", ctypes.c_void_p),
+        ("alibi_slopes", ctypes.c_void_p),
+        ("softcap", ctypes.c_float),
+        ("reserved2", ctypes.c_float),
     ]
 
 

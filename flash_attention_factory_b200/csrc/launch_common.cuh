@@ -192,6 +192,8 @@ AttnArgs make_attn_args(const pa_params *p) {
   a.sm_scale_log2 = p->sm_scale * kLog2e;
   a.k_scale_per_head = (KV == KV_F16) ? nullptr : p->k_scale_per_head;
   a.v_scale_per_head = (KV == KV_F16) ? nullptr : p->v_scale_per_head;
+  a.alibi_slopes = p->alibi_slopes;
+  a.softcap = (p->softcap > 0.f) ? p->softcap : 0.f;
   return a;
 }
 

@@ -75,6 +75,11 @@ struct AttnArgs {
   const float *k_scale_per_head;
   const float *v_scale_per_head;
   float sm_scale_log2;       // sm_scale * log2(e)
+  // opt-in score modifiers (off in the reference, whose call sites are commented out,
+  // paged_attention_kernel_loop.hpp:329-342): soft-cap s -> cap * tanh(s / cap), then an ALiBi
+  // bias slope[h] * (t - (ctx - 1)) on the score of token t
+  const float *alibi_slopes; // fp32 [num_heads] or null
+  float softcap;             // > 0 enables the soft-cap
 };
 
 constexpr float kLn2 = 0.6931471805599453f;
@@ -129,6 +134,7 @@ struct WorkItem {
   uint32_t linear; // item number (split mode), see SplitCursor
   uint32_t seq, head_base, partition;
   uint32_t tok_begin, tok_end;
+  uint32_t ctx; // context length of the sequence
   bool valid;
 };
 
@@ -195,6 +201,7 @@ struct SplitCursor {
     it.head_base = (within - it.partition * groups) * args.hpc;
     it.tok_begin = it.partition * PARTITION;
     it.tok_end = min(ctx, it.tok_begin + PARTITION);
+    it.ctx = ctx;
     it.valid = true;
     return it;
   }
@@ -283,6 +290,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t stages_per_rank = divide_round_up(total_stages, num_ranks);
     first.tok_begin = min(ctx, cta_rank * stages_per_rank * tps);
     first.tok_end = min(ctx, (cta_rank + 1) * stages_per_rank * tps);
+    first.ctx = ctx;
     first.valid = true;
   }
 
@@ -495,6 +503,13 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
                               : args.scale_log2;
       const float out_scale = (args.v_scale_per_head != nullptr) ? __ldg(args.v_scale_per_head + kv_head)
                                                                  : args.out_scale;
+      const bool modifiers = (args.alibi_slopes != nullptr) || (args.softcap > 0.f);
+      float slope[2] = {0.f, 0.f}; // ALiBi slopes of query columns 2*t4, 2*t4+1
+      if (args.alibi_slopes != nullptr) {
+#pragma unroll
+        for (uint32_t j = 0; j < 2; ++j)
+          if (2 * t4 + j < G) slope[j] = __ldg(args.alibi_slopes + kv_head * G + 2 * t4 + j);
+      }
 
       m_ref[0] = m_ref[1] = m_true[0] = m_true[1] = neg_infinity();
       l_run[0] = l_run[1] = 0.f; // per-lane partial sums; reduced over gid at the end
@@ -554,7 +569,30 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           } else {
             cb[0] = cb[1] = cb[2] = cb[3] = neg_infinity();
           }
-          if (n_a < 16u || (act_b && n_b < 16u)) {
+          float eff_scale = scale;
+          if (modifiers) {
+            // soft-cap / ALiBi: turn the raw dot products into log2-domain logits here; the
+            // softmax below then runs with a unit scale
+            const float nat = scale * kLn2; // sm_scale * k scale
+            const int32_t last = static_cast<int32_t>(cur.ctx) - 1;
+            const int32_t t_a = static_cast<int32_t>(cur.tok_begin + tok_a + gid);
+            const int32_t t_b = t_a + static_cast<int32_t>(tps);
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+              const int32_t row = (j >> 1) * 8; // [2],[3] belong to token gid + 8
+              float xa = ca[j] * nat, xb = cb[j] * nat;
+              if (args.softcap > 0.f) {
+                xa = args.softcap * tanhf(xa / args.softcap);
+                xb = args.softcap * tanhf(xb / args.softcap);
+              }
+              xa += slope[j & 1u] * static_cast<float>(t_a + row - last);
+              xb += slope[j & 1u] * static_cast<float>(t_b + row - last);
+              ca[j] = xa * kLog2e;
+              cb[j] = act_b ? xb * kLog2e : neg_infinity();
+            }
+            eff_scale = 1.f;
+          }
+          if (modifiers || n_a < 16u || (act_b && n_b < 16u)) {
             // tokens past the context never count, whatever the cache holds there
             // (reference paged_attention_kernel_loop.hpp:323-327)
             if (gid >= n_a) ca[0] = ca[1] = neg_infinity();
@@ -564,8 +602,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           }
           // ---- online softmax (reference paged_attention_kernel_loop.hpp:382-419);
           // scale > 0, so the maximum commutes with the scaling
-          m_true[0] = fmaxf(m_true[0], quad_column_max(fmaxf(fmaxf(ca[0], ca[2]), fmaxf(cb[0], cb[2]))) * scale);
-          m_true[1] = fmaxf(m_true[1], quad_column_max(fmaxf(fmaxf(ca[1], ca[3]), fmaxf(cb[1], cb[3]))) * scale);
+          m_true[0] = fmaxf(m_true[0], quad_column_max(fmaxf(fmaxf(ca[0], ca[2]), fmaxf(cb[0], cb[2]))) * eff_scale);
+          m_true[1] = fmaxf(m_true[1], quad_column_max(fmaxf(fmaxf(ca[1], ca[3]), fmaxf(cb[1], cb[3]))) * eff_scale);
           const bool stale = (m_true[0] > m_ref[0] + kRescaleThreshold) ||
                              (m_true[1] > m_ref[1] + kRescaleThreshold);
           if (__any_sync(0xffffffffu, stale)) {
@@ -586,8 +624,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           float pa[4], pb[4];
 #pragma unroll
           for (uint32_t j = 0; j < 4; ++j) {
-            pa[j] = fast_exp2(fmaf(ca[j], scale, -m_ref[j & 1u]));
-            pb[j] = fast_exp2(fmaf(cb[j], scale, -m_ref[j & 1u]));
+            pa[j] = fast_exp2(fmaf(ca[j], eff_scale, -m_ref[j & 1u]));
+            pb[j] = fast_exp2(fmaf(cb[j], eff_scale, -m_ref[j & 1u]));
           }
           l_run[0] += (pa[0] + pa[2]) + (pb[0] + pb[2]); // fp32 sum of the unrounded weights
           l_run[1] += (pa[1] + pa[3]) + (pb[1] + pb[3]);

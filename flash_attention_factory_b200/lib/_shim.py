@@ -34,7 +34,8 @@ def _kv_dtype_of(cache: torch.Tensor, fp8: bool) -> int:
 def build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
                  value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
                  fp8_scale, block_size, max_context_len, alibi_slopes, sinks, softcap,
-                 fp8: bool, k_scale_per_head=None, v_scale_per_head=None) -> _cabi.PaParams:
+                 fp8: bool, k_scale_per_head=None, v_scale_per_head=None,
+                 use_alibi: bool = False, use_softcap: bool = False) -> _cabi.PaParams:
     """Validates what the reference's ``data_ptr<float>()`` calls would and fills pa_params.
 
     ``debug_output``, ``alibi_slopes``, ``softcap`` are accepted and ignored like in the
@@ -95,6 +96,13 @@ def build_params(max_logits, exp_sums, tem_output, output, debug_output, query, 
             _require(t.dtype == torch.float32 and t.is_contiguous() and t.device == query.device
                      and t.numel() == key_cache.size(2), f"{name} must be float32 [num_kv_heads] on the device")
             setattr(p, name, t.data_ptr())
+    # opt-in only: by default alibi_slopes and softcap are ignored, as in the reference
+    if use_alibi:
+        _require(alibi_slopes.is_cuda and alibi_slopes.is_contiguous()
+                 and alibi_slopes.numel() == query.size(1), "alibi_slopes must be float32 [num_heads] on the device")
+        p.alibi_slopes = alibi_slopes.data_ptr()
+    if use_softcap and softcap > 0:
+        p.softcap = float(softcap)
     return p
 
 

@@ -26,7 +26,8 @@ def run(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache
 
 def enqueue(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
             block_tables, context_lens, num_queries_per_tokens, sm_scale, fp8_scale, block_size,
-            max_context_len, alibi_slopes, sinks, softcap, *, k_scale_per_head=None, v_scale_per_head=None):
+            max_context_len, alibi_slopes, sinks, softcap, *, k_scale_per_head=None, v_scale_per_head=None,
+            use_alibi=False, use_softcap=False):
     """Same arguments as ``run`` but asynchronous on the current stream (returns nothing).
 
     ``k_scale_per_head`` / ``v_scale_per_head`` (float32 [num_kv_heads], optional, no reference
@@ -34,6 +35,7 @@ def enqueue(max_logits, exp_sums, tem_output, output, debug_output, query, key_c
     p = _shim.build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
                            value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
                            fp8_scale, block_size, max_context_len, alibi_slopes, sinks, softcap,
-                           fp8=True, k_scale_per_head=k_scale_per_head, v_scale_per_head=v_scale_per_head)
+                           fp8=True, k_scale_per_head=k_scale_per_head, v_scale_per_head=v_scale_per_head,
+                           use_alibi=use_alibi, use_softcap=use_softcap)
     _shim.check_scratch(p, max_logits, exp_sums, tem_output)
     _shim.enqueue_entry(_ENTRY, p, query.device)

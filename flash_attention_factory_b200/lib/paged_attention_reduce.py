@@ -23,10 +23,14 @@ def run(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache
 
 def enqueue(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
             block_tables, context_lens, num_queries_per_tokens, sm_scale, block_size,
-            max_context_len, alibi_slopes, sinks, softcap):
-    """Same arguments as ``run`` but asynchronous on the current stream (returns nothing)."""
+            max_context_len, alibi_slopes, sinks, softcap, *, use_alibi=False, use_softcap=False):
+    """Same arguments as ``run`` but asynchronous on the current stream (returns nothing).
+
+    ``use_alibi`` / ``use_softcap`` (no reference counterpart) make ``alibi_slopes`` / ``softcap``
+    live; by default both are ignored, as the reference ignores them."""
     p = _shim.build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
                            value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
-                           1.0, block_size, max_context_len, alibi_slopes, sinks, softcap, fp8=False)
+                           1.0, block_size, max_context_len, alibi_slopes, sinks, softcap, fp8=False,
+                           use_alibi=use_alibi, use_softcap=use_softcap)
     _shim.check_scratch(p, max_logits, exp_sums, tem_output)
     _shim.enqueue_entry(_ENTRY, p, query.device)

@@ -94,6 +94,15 @@ typedef struct pa_params {
    * fp16(code) * v_scale_per_head[k], and fp8_scale is not used for that cache. */
   const float *k_scale_per_head;
   const float *v_scale_per_head;
+  /* Opt-in score modifiers.  The reference accepts alibi_slopes and softcap and ignores
+   * them (call sites commented out, paged_attention_kernel_loop.hpp:329-342), and so do the
+   * Python run() shims; a caller of this ABI enables them by setting these fields:
+   * score s of token t becomes softcap * tanh(s / softcap) if softcap > 0 (the formula of
+   * the reference oracle, test_paged.py:92-95), then + alibi_slopes[h] * (t - (ctx - 1)) if
+   * alibi_slopes != NULL (fp32 [num_heads], device pointer). */
+  const float *alibi_slopes;
+  float softcap;
+  float reserved2;
 } pa_params;
 
 /* Tiling knobs of include/paged_attention_policy_v2.hpp for one

@@ -56,7 +56,8 @@ def gather_sequence(cache_paged: torch.Tensor, block_table_row: torch.Tensor, co
 
 
 def attention_one_sequence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
-                           sinks: Optional[torch.Tensor], sm_scale: Optional[float]) -> torch.Tensor:
+                           sinks: Optional[torch.Tensor], sm_scale: Optional[float],
+                           softcap: float = 0.0, alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """fp32 attention of one decode token: q [H, D], k/v [T, HK, D] (fp32) -> [H, D] fp32.
 
     Follows attention_ref with upcast=True (test_paged.py:82-123,165): GQA repeat of K/V,
@@ -72,6 +73,14 @@ def attention_one_sequence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     v = v.repeat_interleave(g, dim=1)
     qs = q / math.sqrt(d) if sm_scale is None else q * sm_scale  # test_paged.py:89
     scores = torch.einsum("hd,shd->hs", qs, k)
+    if softcap > 0:
+        scores = (scores / softcap).tanh() * softcap  # test_paged.py:92-95
+    if alibi_slopes is not None:
+        # attn_bias of a decode token at position t-1 (test_paged.py:109-110 adds attn_bias; the
+        # helper that would build it from slopes is not defined in the reference, so the usual
+        # ALiBi form is taken: -slope * distance to the query position)
+        dist = torch.arange(t, dtype=torch.float32) - float(t - 1)
+        scores = scores + alibi_slopes.to(torch.float32).reshape(h, 1) * dist.reshape(1, t)
     smax = scores.max(dim=-1, keepdim=True).values
     if sinks is not None:
         sk = sinks.to(torch.float32).reshape(h, 1)
@@ -89,7 +98,8 @@ def paged_attention_ref(query: torch.Tensor, key_cache: torch.Tensor, value_cach
                         block_tables: torch.Tensor, context_lens: Sequence[int],
                         sm_scale: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
                         fp8_scale: float = 1.0, k_scales: Optional[torch.Tensor] = None,
-                        v_scales: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        v_scales: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                        alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Reference result of all four entry points: fp16 [num_seqs, num_heads, head_size].
 
     `k_scales` / `v_scales` ([kv_heads] each) replace `fp8_scale` for K / V when given.
@@ -106,7 +116,7 @@ def paged_attention_ref(query: torch.Tensor, key_cache: torch.Tensor, value_cach
                              fp8_scale if k_scales is None else k_scales)
         v = dequantize_cache(gather_sequence(value_cache, block_tables[i], lens[i]),
                              fp8_scale if v_scales is None else v_scales)
-        o = attention_one_sequence(query[i].to(torch.float32), k, v, sinks, sm_scale)
+        o = attention_one_sequence(query[i].to(torch.float32), k, v, sinks, sm_scale, softcap, alibi_slopes)
         out[i] = o.to(torch.float16)  # test_paged.py:168
     return out
 
