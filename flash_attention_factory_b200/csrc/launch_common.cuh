@@ -231,7 +231,12 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
     const uint64_t items = static_cast<uint64_t>(p->num_kv_heads / args.hpc) * p->max_num_partitions * p->num_seqs;
     const uint64_t resident = static_cast<uint64_t>(policy::ctas_per_sm) * static_cast<uint64_t>(dev.sm_count);
     cfg.gridDim = dim3(static_cast<unsigned>(items < resident ? items : resident), 1, 1);
-    cfg.numAttrs = 0;
+    // programmatic dependent launch: back-to-back calls overlap this grid's start-up with the
+    // previous kernel's tail (the kernel blocks in griddepcontrol.wait before its first read)
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
   } else {
     const uint32_t cs = choose_cluster_size(p, args.hpc, dev.sm_count, args.tokens_per_stage);
     cfg.gridDim = dim3(cs, p->num_kv_heads / args.hpc, p->num_seqs);

@@ -274,6 +274,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     // let the merge kernel's CTAs be scheduled as this grid's CTAs retire (it waits for the
     // completion of this grid before it reads anything)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // this grid may itself have been scheduled while the previous kernel of the stream was
+    // draining: nothing in global memory is touched before that kernel has completed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     cursor.init(args, head_groups, lane);
     first = cursor.seek(blockIdx.x, args, head_groups, lane);
   } else {
@@ -902,6 +905,7 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
   const uint32_t tid = threadIdx.x;
   // Launched with programmatic stream serialization, this grid may start while the attention
   // kernel drains; nothing is read before that kernel has completed and its writes are visible.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t ctx = context_lens[seq];
   const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
@@ -1004,6 +1008,7 @@ merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict_
   constexpr uint32_t ROWS = 128 / (D / 4);  // residue classes of the CTA-per-pair kernel
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t pair = blockIdx.x * 4 + (threadIdx.x >> 5); // seq * num_heads + head
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (pair >= num_pairs) return;
   const uint32_t seq = pair / num_heads;
@@ -1012,16 +1017,33 @@ merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict_
   const size_t base = static_cast<size_t>(pair) * max_num_partitions;
   const __half *rows = tmp_out + base * D + lane * DPL;
 
-  float m = neg_infinity();
-  for (uint32_t p = lane; p < np; p += 32) m = fmaxf(m, max_logits[base + p]);
+  // the first 32 partitions' statistics live in registers, one partition per lane; their
+  // rows are requested right away, before the weights are known
+  const bool mine = lane < np;
+  const float ml_lane = mine ? __ldg(max_logits + base + lane) : neg_infinity();
+  const float es_lane = mine ? __ldg(exp_sums + base + lane) : 0.f;
+  constexpr uint32_t PREFETCH = 2 * ROWS;
+  uint2 pre[PREFETCH];
+#pragma unroll
+  for (uint32_t u = 0; u < PREFETCH; ++u) {
+    pre[u] = make_uint2(0u, 0u);
+    if (u < np) {
+      if constexpr (DPL == 4) pre[u] = __ldg(reinterpret_cast<const uint2 *>(rows + static_cast<size_t>(u) * D));
+      else pre[u].x = __ldg(reinterpret_cast<const uint32_t *>(rows + static_cast<size_t>(u) * D));
+    }
+  }
+  float m = ml_lane;
+  for (uint32_t p = lane + 32; p < np; p += 32) m = fmaxf(m, max_logits[base + p]);
 #pragma unroll
   for (uint32_t o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   // total weight: chunk c plays warp c of the CTA-per-pair kernel (threads 32c .. 32c+31)
+  const float w_lane = mine ? es_lane * __expf(ml_lane - m) : 0.f;
   float wsum = 0.f;
 #pragma unroll
   for (uint32_t c = 0; c < 4; ++c) {
-    float part = 0.f;
-    for (uint32_t p = 32 * c + lane; p < np; p += 128) part += exp_sums[base + p] * __expf(max_logits[base + p] - m);
+    float part = (c == 0) ? w_lane : 0.f;
+    for (uint32_t p = 32 * c + lane + (c == 0 ? 128u : 0u); p < np; p += 128)
+      part += exp_sums[base + p] * __expf(max_logits[base + p] - m);
 #pragma unroll
     for (uint32_t o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
     wsum = (c == 0) ? part : wsum + part;
@@ -1033,7 +1055,23 @@ merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict_
   for (uint32_t r = 0; r < ROWS; ++r)
 #pragma unroll
     for (uint32_t i = 0; i < DPL; ++i) acc[r][i] = 0.f;
-  for (uint32_t p0 = 0; p0 < np; p0 += ROWS) {
+  auto add_row = [&](uint32_t r, uint2 raw, float w) {
+    const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+    acc[r][0] += w * v01.x;
+    acc[r][1] += w * v01.y;
+    if constexpr (DPL == 4) {
+      const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+      acc[r][2] += w * v23.x;
+      acc[r][3] += w * v23.y;
+    }
+  };
+  // partitions 0 .. PREFETCH-1 from the prefetched rows (weights come from the owning lane)
+#pragma unroll
+  for (uint32_t u = 0; u < PREFETCH; ++u) {
+    const float w = __shfl_sync(0xffffffffu, w_lane, u) * inv_w;
+    if (u < np) add_row(u % ROWS, pre[u], w);
+  }
+  for (uint32_t p0 = PREFETCH; p0 < np; p0 += ROWS) {
 #pragma unroll
     for (uint32_t r = 0; r < ROWS; ++r) {
       const uint32_t p = p0 + r;
@@ -1042,14 +1080,7 @@ merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict_
         uint2 raw = make_uint2(0u, 0u);
         if constexpr (DPL == 4) raw = __ldg(reinterpret_cast<const uint2 *>(rows + static_cast<size_t>(p) * D));
         else raw.x = __ldg(reinterpret_cast<const uint32_t *>(rows + static_cast<size_t>(p) * D));
-        const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-        acc[r][0] += w * v01.x;
-        acc[r][1] += w * v01.y;
-        if constexpr (DPL == 4) {
-          const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-          acc[r][2] += w * v23.x;
-          acc[r][3] += w * v23.y;
-        }
+        add_row(r, raw, w);
       }
     }
   }
