@@ -327,10 +327,12 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "kvwrite"],
+                    help="c1..c5: BASELINE configs of the attention path; kvwrite: the cache-append kernel")
     ap.add_argument("--variant", default=None, choices=["loop", "reduce", "auto"],
                     help="override the entry point the configuration names")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--fp8-scale", type=float, default=0.05, help="kvwrite: per-tensor scale of the cache")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cuda-graph", action="store_true",
                     help="record one call per rotated cache copy into CUDA graphs and replay them "
@@ -349,6 +351,10 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if a.config == "kvwrite":
+        if rank == 0:
+            bench_cache_write(a)
+        return
     spec = config_spec(a.config)
     if a.num_seqs is not None:
         spec["num_seqs"] = a.num_seqs
@@ -507,6 +513,49 @@ TRAFFIC_BYTES: dict = {
     # profiles/paged_attention_kernel_split_e4m3_c4_small.md: 8 x (134.31 + 4.09) MB
     ("c4", "reduce"): 1_107_200_000,
 }
+
+
+def bench_cache_write(a) -> None:
+    """`--config kvwrite`: pa_reshape_and_cache on 64k new tokens of a Llama-3-8B-shaped cache
+    (8 KV heads x 128, block 16), fp16 input -> e4m3 cache.  HBM-bound: per token it reads
+    2 x 2 KB of fp16 K/V and writes 2 x 1 KB of FP8."""
+    from flash_attention_factory_b200.cache_ops import reshape_and_cache
+
+    dev = torch.device("cuda", 0)
+    tokens, hk, d, bs = 65536, 8, 128, 16
+    kv = a.kv or "float8_e4m3fn"
+    dt = {"float16": torch.float16, "float8_e5m2": torch.float8_e5m2, "float8_e4m3fn": torch.float8_e4m3fn}[kv]
+    g = torch.Generator(device=dev).manual_seed(0)
+    key = torch.randn(tokens, hk, d, generator=g, device=dev, dtype=torch.float16)
+    value = torch.randn(tokens, hk, d, generator=g, device=dev, dtype=torch.float16)
+    nb = 2 * tokens // bs
+    kc = torch.zeros(nb, bs, hk, d, device=dev, dtype=torch.float16).to(dt)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(nb * bs, generator=g, device=dev)[:tokens].to(torch.int64)
+    elt = 2 if kv == "float16" else 1
+    nbytes = tokens * hk * d * (2 * 2 + 2 * elt)
+    for _ in range(max(3, a.warmup)):
+        reshape_and_cache(key, value, kc, vc, slots, a.fp8_scale)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        reshape_and_cache(key, value, kc, vc, slots, a.fp8_scale)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / a.steps
+    peak, kind = measured_hbm_peak()
+    val = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "kv_cache_write_GBps", "value": round(val, 1), "unit": "GB/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": max(3, a.warmup), "ms_per_step": round(ms, 5), "higher_is_better": True,
+        "dtype": f"fp16 -> {kv}", "data": "synthetic",
+        "config": {"workload": f"pa_reshape_and_cache: {tokens} tokens, {hk} KV heads x {d}, block {bs}, "
+                               f"random slots, cache {kv}; {nbytes} bytes moved per call (402 MB, larger than L2)"},
+        "roofline": {"bound": "hbm", "kernel": "reshape_and_cache_kernel", "achieved": round(val, 1),
+                     "peak": peak, "unit": "GB/s", "frac": round(val / peak, 4), "peak_kind": f"of {kind}",
+                     "traffic": None},
+        "gpu_launches": a.steps}), flush=True)
 
 
 def cpu_baseline(w: Workload) -> dict:

@@ -9,13 +9,18 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <cmath>
+
 #include "launch_common.cuh"
 
 namespace pa {
 
 // 8 fp16 values (one 16-byte load) -> 8 cache elements
+// `exact_rcp` != 0 means 1 / scale is a power of two, so multiplying by it is exact and
+// equals the division bit for bit; otherwise an IEEE division keeps the torch arithmetic.
 template <int KV>
-__device__ __forceinline__ void store_converted(void *dst_row, uint32_t elem, uint4 v, float scale) {
+__device__ __forceinline__ void store_converted(void *dst_row, uint32_t elem, uint4 v, float scale,
+                                                float exact_rcp) {
   if constexpr (KV == KV_F16) {
     *reinterpret_cast<uint4 *>(static_cast<__half *>(dst_row) + elem) = v;
   } else {
@@ -25,13 +30,17 @@ __device__ __forceinline__ void store_converted(void *dst_row, uint32_t elem, ui
     for (int i = 0; i < 2; ++i) {
       // IEEE division in fp32, then one rounding to FP8: the arithmetic of
       // (x.float() / scale).to(float8) for every value inside the format's range
-      const float2 a = __half22float2(h[2 * i]);
-      const float2 b = __half22float2(h[2 * i + 1]);
+      float2 a = __half22float2(h[2 * i]);
+      float2 b = __half22float2(h[2 * i + 1]);
       constexpr __nv_fp8_interpretation_t fmt = (KV == KV_E5M2) ? __NV_E5M2 : __NV_E4M3;
-      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(a.x, scale), __fdiv_rn(a.y, scale)),
-                                                   __NV_SATFINITE, fmt);
-      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(b.x, scale), __fdiv_rn(b.y, scale)),
-                                                   __NV_SATFINITE, fmt);
+      if (exact_rcp != 0.f) {
+        a.x *= exact_rcp; a.y *= exact_rcp; b.x *= exact_rcp; b.y *= exact_rcp;
+      } else {
+        a.x = __fdiv_rn(a.x, scale); a.y = __fdiv_rn(a.y, scale);
+        b.x = __fdiv_rn(b.x, scale); b.y = __fdiv_rn(b.y, scale);
+      }
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(a, __NV_SATFINITE, fmt);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(b, __NV_SATFINITE, fmt);
       packed[i] = lo | (hi << 16);
     }
     *reinterpret_cast<uint2 *>(static_cast<uint8_t *>(dst_row) + elem) = make_uint2(packed[0], packed[1]);
@@ -44,7 +53,7 @@ __global__ void __launch_bounds__(128)
 reshape_and_cache_kernel(const __half *__restrict__ key, const __half *__restrict__ value,
                          void *__restrict__ key_cache, void *__restrict__ value_cache,
                          const int64_t *__restrict__ slot_mapping, uint32_t row_elems, uint64_t num_slots,
-                         float scale) {
+                         float scale, float exact_rcp) {
   const uint32_t token = blockIdx.x;
   const int64_t slot = slot_mapping[token];
   if (slot < 0 || static_cast<uint64_t>(slot) >= num_slots) return; // padding token / out of range
@@ -56,8 +65,8 @@ reshape_and_cache_kernel(const __half *__restrict__ key, const __half *__restric
   for (uint32_t e = threadIdx.x * 8; e < row_elems; e += blockDim.x * 8) {
     const uint4 kv = __ldg(reinterpret_cast<const uint4 *>(ksrc + e));
     const uint4 vv = __ldg(reinterpret_cast<const uint4 *>(vsrc + e));
-    store_converted<KV>(kdst, e, kv, scale);
-    store_converted<KV>(vdst, e, vv, scale);
+    store_converted<KV>(kdst, e, kv, scale, exact_rcp);
+    store_converted<KV>(vdst, e, vv, scale, exact_rcp);
   }
 }
 
@@ -80,17 +89,24 @@ extern "C" PA_API int pa_reshape_and_cache(const pa_cache_write_params *p, void 
   if (!aligned16(p->key) || !aligned16(p->value) || !aligned16(p->key_cache) || !aligned16(p->value_cache))
     return fail(PA_ERR_BAD_ARG, "key / value / caches must be 16-byte aligned");
   const uint64_t num_slots = p->num_blocks * p->block_size;
+  // a power-of-two scale (1.0 included) has an exact reciprocal: no division needed
+  float exact_rcp = 0.f;
+  {
+    int exponent = 0;
+    if (p->kv_dtype != PA_KV_F16 && std::frexp(p->fp8_scale, &exponent) == 0.5f && exponent > -100 && exponent < 100)
+      exact_rcp = 1.f / p->fp8_scale;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid(p->num_tokens), block(128);
   const uint32_t re = static_cast<uint32_t>(row_elems);
   const __half *k = static_cast<const __half *>(p->key);
   const __half *v = static_cast<const __half *>(p->value);
   if (p->kv_dtype == PA_KV_F16)
-    reshape_and_cache_kernel<KV_F16><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, 1.f);
+    reshape_and_cache_kernel<KV_F16><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, 1.f, 1.f);
   else if (p->kv_dtype == PA_KV_FP8_E5M2)
-    reshape_and_cache_kernel<KV_E5M2><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, p->fp8_scale);
+    reshape_and_cache_kernel<KV_E5M2><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, p->fp8_scale, exact_rcp);
   else
-    reshape_and_cache_kernel<KV_E4M3><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, p->fp8_scale);
+    reshape_and_cache_kernel<KV_E4M3><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, p->fp8_scale, exact_rcp);
   PA_CUDA_TRY(cudaGetLastError());
   return PA_OK;
 }

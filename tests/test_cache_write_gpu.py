@@ -13,7 +13,8 @@ def _bits(t):
 
 
 @pytest.mark.parametrize("kv,scale", [("float16", 1.0), ("float8_e5m2", 1.0), ("float8_e4m3fn", 1.0),
-                                      ("float8_e4m3fn", 0.0123), ("float8_e5m2", 3.0)])
+                                      ("float8_e4m3fn", 0.0123), ("float8_e5m2", 3.0),
+                                      ("float8_e4m3fn", 0.25), ("float8_e5m2", 8.0)])
 @pytest.mark.parametrize("hk,d,bs", [(8, 128, 16), (2, 64, 64), (1, 128, 32)])
 def test_append_is_bit_exact(cuda_device, kv, scale, hk, d, bs):
     from flash_attention_factory_b200.cache_ops import reshape_and_cache
