@@ -6,6 +6,7 @@
 // paged_attention_reduce/launch_kernels_reduce.h:18-78,80-197).
 #pragma once
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -207,6 +208,10 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
   if (dev.cc_major < 10) return fail(PA_ERR_CUDA, "this library needs an sm_100a device");
 
   AttnArgs args = make_attn_args<D, KV>(p);
+  if (MODE == MODE_SPLIT) {
+    static std::atomic<uint32_t> next_slot{0}; // per kernel instantiation, like its counters
+    args.sched_slot = next_slot.fetch_add(1, std::memory_order_relaxed) % kSchedSlots;
+  }
   CUtensorMap map_k, map_v;
   if (int rc = encode_cache_map<D, KV>(&map_k, p->key_cache, p, args.rows_per_box, args.heads_per_box)) return rc;
   if (int rc = encode_cache_map<D, KV>(&map_v, p->value_cache, p, args.rows_per_box, args.heads_per_box)) return rc;

@@ -47,6 +47,13 @@ enum Mode : int { MODE_LOOP = 0, MODE_SPLIT = 1 };
 // One copy per translation unit (the launchers are compiled separately).
 static __device__ int g_pa_device_status = 0;
 
+// Work counters of the split kernel's dynamic scheduler: [slot][0] hands out item numbers,
+// [slot][1] counts retired CTAs; the last CTA of a launch zeroes its slot again.  The host
+// gives consecutive launches consecutive slots, so launches that overlap in time (other
+// streams, programmatic dependent launch) never share one.
+constexpr uint32_t kSchedSlots = 1024;
+static __device__ unsigned int g_sched[kSchedSlots][2];
+
 struct AttnArgs {
   const __half *query;
   __half *out;
@@ -75,6 +82,7 @@ struct AttnArgs {
   const float *k_scale_per_head;
   const float *v_scale_per_head;
   float sm_scale_log2;       // sm_scale * log2(e)
+  uint32_t sched_slot;       // row of g_sched this launch uses (split mode)
   // opt-in score modifiers (off in the reference, whose call sites are commented out,
   // paged_attention_kernel_loop.hpp:329-342): soft-cap s -> cap * tanh(s / cap), then an ALiBi
   // bias slope[h] * (t - (ctx - 1)) on the score of token t
@@ -109,7 +117,10 @@ struct SmemLayout {
   static constexpr uint32_t WARP_STATS_FLOATS = 3 * NW * 8;
   static constexpr uint32_t WARP_STATS_BYTES = 2 * WARP_STATS_FLOATS * 4;
   static constexpr uint32_t BAR_OFFSET = WARP_STATS_OFFSET + WARP_STATS_BYTES;
-  static constexpr uint32_t TOTAL_BYTES = BAR_OFFSET + 2 * NSTAGES * 8 + 16;
+  // after the ring barriers: abort flag (16 B), then the item queue between the producer and
+  // the consumers: two entries, each an item number and a full / empty mbarrier pair
+  static constexpr uint32_t SCHED_OFFSET = BAR_OFFSET + 2 * NSTAGES * 8 + 16;
+  static constexpr uint32_t TOTAL_BYTES = SCHED_OFFSET + 4 * 8 + 16;
   static constexpr uint32_t DYN_SMEM = TOTAL_BYTES + 1024; // slack for 1024-byte alignment
   // loop mode: every warp parks (O[8][D], m[8], l[8]) on the (by then idle) ring for the
   // cluster-wide merge
@@ -182,6 +193,7 @@ struct SplitCursor {
                                            uint32_t lane) {
     WorkItem it{};
     it.valid = false;
+    if (index < items_before) init(args, groups, lane); // never happens with increasing numbers
     while (index >= items_before + window_items) {
       if (window_seq + 32 >= args.num_seqs) return it; // past the last item
       items_before += window_items;
@@ -258,6 +270,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   uint64_t *empty_bar = full_bar + NSTAGES;
   volatile uint32_t *abort_flag =
       reinterpret_cast<volatile uint32_t *>(smem + L::BAR_OFFSET + 2 * NSTAGES * 8);
+  uint64_t *sched_full = reinterpret_cast<uint64_t *>(smem + L::SCHED_OFFSET); // [2]
+  uint64_t *sched_empty = sched_full + 2;                                       // [2]
+  volatile uint32_t *sched_item = reinterpret_cast<volatile uint32_t *>(sched_full + 4); // [2]
+  constexpr uint32_t kNoItem = 0xffffffffu;
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
@@ -302,6 +318,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       mbar_init(&full_bar[s], 1);   // one arrive.expect_tx by the producer
       mbar_init(&empty_bar[s], NW); // one arrive per consumer warp
     }
+    for (uint32_t s = 0; s < 2; ++s) {
+      mbar_init(&sched_full[s], 1);
+      mbar_init(&sched_empty[s], NW);
+    }
     *abort_flag = 0u;
     mbar_fence_init();
   }
@@ -336,11 +356,29 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
 
     WorkItem cur = first;
     uint32_t block_id_next = fetch_block_id(cur, lane_chunk);
+    uint32_t item_no = 0;
     while (cur.valid && alive) {
       WorkItem nxt{};
       nxt.valid = false;
-      if constexpr (MODE == MODE_SPLIT)
-        nxt = cursor.seek(cur.linear + gridDim.x, args, head_groups, lane);
+      if constexpr (MODE == MODE_SPLIT) {
+        // Dynamic scheduling: the CTA's first item is its block index, every further one is
+        // drawn from a global counter, so CTAs that run faster take more items.  The number
+        // is published to the consumer warps through a two-entry queue in shared memory.
+        uint32_t next_index = 0;
+        if (lane == 0) next_index = gridDim.x + atomicAdd(&g_sched[args.sched_slot][0], 1u);
+        next_index = __shfl_sync(0xffffffffu, next_index, 0);
+        nxt = cursor.seek(next_index, args, head_groups, lane);
+        const uint32_t entry = item_no + 1, qs = entry & 1u, use = (entry - 1u) >> 1; // n-th use of the slot
+        if (lane == 0) {
+          alive = mbar_wait_bounded(&sched_empty[qs], (use & 1u) ^ 1u, abort_flag);
+          if (alive) {
+            sched_item[qs] = nxt.valid ? next_index : kNoItem;
+            mbar_arrive(&sched_full[qs]);
+          }
+        }
+        alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+        if (!alive) break;
+      }
       const uint32_t total_chunks = divide_round_up(cur.tok_end - cur.tok_begin, rows);
       const int32_t head_coord = static_cast<int32_t>(cur.head_base + lane_head);
       for (uint32_t chunk0 = 0; chunk0 < total_chunks && alive; chunk0 += chunks_per_batch) {
@@ -385,6 +423,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
       }
       cur = nxt;
+      ++item_no;
     }
   } else {
     // =========================== consumer warps ==========================
@@ -494,11 +533,23 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     float m_ref[2], m_true[2], l_run[2];
     float acc[KSTEPS][4];
 
+    uint32_t item_no = 0;
     while (cur.valid) {
       WorkItem nxt{};
       nxt.valid = false;
-      if constexpr (MODE == MODE_SPLIT)
-        nxt = cursor.seek(cur.linear + gridDim.x, args, head_groups, lane);
+      if constexpr (MODE == MODE_SPLIT) {
+        // the producer has published the number of the next item (or "none") before it
+        // started to load this one
+        const uint32_t entry = item_no + 1, qs = entry & 1u, use = (entry - 1u) >> 1; // n-th use of the slot
+        if (*abort_flag != 0u) alive = false;
+        uint32_t next_index = kNoItem;
+        if (alive) alive = mbar_wait_bounded(&sched_full[qs], use & 1u, abort_flag);
+        if (alive) next_index = sched_item[qs];
+        __syncwarp();
+        if (alive && lane == 0) mbar_arrive(&sched_empty[qs]);
+        if (next_index != kNoItem) nxt = cursor.seek(next_index, args, head_groups, lane);
+        ++item_no;
+      }
       const uint32_t kv_head = cur.head_base + my_head;
       // softmax scale (log2 domain) and output scale of this warp's KV head
       const float scale = (args.k_scale_per_head != nullptr)
@@ -876,6 +927,18 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       }
     }
     cluster.sync(); // peers may still be reading this CTA's shared memory
+  }
+  if constexpr (MODE == MODE_SPLIT) {
+    if (threadIdx.x == 0) {
+      // retire: the last CTA of the launch hands the counters back zeroed
+      __threadfence();
+      const unsigned int done = atomicAdd(&g_sched[args.sched_slot][1], 1u);
+      if (done == gridDim.x - 1) {
+        g_sched[args.sched_slot][0] = 0u;
+        g_sched[args.sched_slot][1] = 0u;
+        __threadfence();
+      }
+    }
   }
   if (*abort_flag != 0u) {
     __nanosleep(200000); // give copies that are still in flight time to land
