@@ -73,6 +73,7 @@ class PaParams(ctypes.Structure):
         ("alibi_slopes", ctypes.c_void_p),
         ("softcap", ctypes.c_float),
         ("reserved2", ctypes.c_float),
+        ("seq_indices", ctypes.c_void_p),
     ]
 
 

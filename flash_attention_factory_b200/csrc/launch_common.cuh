@@ -193,6 +193,7 @@ AttnArgs make_attn_args(const pa_params *p) {
   a.sm_scale_log2 = p->sm_scale * kLog2e;
   a.k_scale_per_head = (KV == KV_F16) ? nullptr : p->k_scale_per_head;
   a.v_scale_per_head = (KV == KV_F16) ? nullptr : p->v_scale_per_head;
+  a.seq_indices = p->seq_indices;
   a.alibi_slopes = p->alibi_slopes;
   a.softcap = (p->softcap > 0.f) ? p->softcap : 0.f;
   return a;
@@ -284,15 +285,15 @@ int enqueue_merge(const pa_params *p, cudaStream_t stream) {
     PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partitions_warp_kernel<D>, static_cast<__half *>(p->out),
                                    static_cast<const __half *>(p->tmp_out),
                                    static_cast<const float *>(p->max_logits),
-                                   static_cast<const float *>(p->exp_sums), p->context_lens, p->num_heads,
-                                   static_cast<uint32_t>(pairs), p->max_num_partitions, psize));
+                                   static_cast<const float *>(p->exp_sums), p->context_lens, p->seq_indices,
+                                   p->num_heads, static_cast<uint32_t>(pairs), p->max_num_partitions, psize));
     return PA_OK;
   }
   PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partitions_kernel<D>, static_cast<__half *>(p->out),
                                  static_cast<const __half *>(p->tmp_out),
                                  static_cast<const float *>(p->max_logits),
-                                 static_cast<const float *>(p->exp_sums), p->context_lens, p->num_heads,
-                                 p->max_num_partitions, psize));
+                                 static_cast<const float *>(p->exp_sums), p->context_lens, p->seq_indices,
+                                 p->num_heads, p->max_num_partitions, psize));
   return PA_OK;
 }
 

@@ -83,6 +83,9 @@ struct AttnArgs {
   const float *v_scale_per_head;
   float sm_scale_log2;       // sm_scale * log2(e)
   uint32_t sched_slot;       // row of g_sched this launch uses (split mode)
+  // optional list of the sequences this launch covers (num_seqs entries); all tensors are
+  // still indexed by the sequence ids found in the list
+  const uint32_t *seq_indices;
   // opt-in score modifiers (off in the reference, whose call sites are commented out,
   // paged_attention_kernel_loop.hpp:329-342): soft-cap s -> cap * tanh(s / cap), then an ALiBi
   // bias slope[h] * (t - (ctx - 1)) on the score of token t
@@ -164,13 +167,15 @@ template <uint32_t PARTITION>
 struct SplitCursor {
   uint32_t window_seq;     // first sequence of the window (multiple of 32)
   uint32_t items_before;   // items of all sequences before the window
-  uint32_t lane_ctx;       // context length of sequence window_seq + lane (0 past the batch)
+  uint32_t lane_seq;       // id of the (window_seq + lane)-th sequence of the launch
+  uint32_t lane_ctx;       // its context length (0 past the end of the launch)
   uint32_t lane_incl;      // items of sequences window_seq .. window_seq + lane (inclusive scan)
   uint32_t window_items;   // items of the whole window
 
   __device__ __forceinline__ void load_window(const AttnArgs &args, uint32_t groups, uint32_t lane) {
-    const uint32_t seq = window_seq + lane;
-    lane_ctx = (seq < args.num_seqs) ? __ldg(args.context_lens + seq) : 0u;
+    const uint32_t pos = window_seq + lane;
+    lane_seq = (pos < args.num_seqs) ? (args.seq_indices != nullptr ? __ldg(args.seq_indices + pos) : pos) : 0u;
+    lane_ctx = (pos < args.num_seqs) ? __ldg(args.context_lens + lane_seq) : 0u;
     const uint32_t parts = min(divide_round_up(lane_ctx, PARTITION), args.max_num_partitions);
     uint32_t v = parts * groups;
 #pragma unroll
@@ -208,7 +213,7 @@ struct SplitCursor {
     const uint32_t parts = min(divide_round_up(ctx, PARTITION), args.max_num_partitions);
     const uint32_t within = local - (incl - parts * groups); // item number inside the sequence
     it.linear = index;
-    it.seq = window_seq + owner;
+    it.seq = __shfl_sync(0xffffffffu, lane_seq, owner);
     it.partition = within / groups;
     it.head_base = (within - it.partition * groups) * args.hpc;
     it.tok_begin = it.partition * PARTITION;
@@ -300,7 +305,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     cg::cluster_group cluster = cg::this_cluster();
     cta_rank = cluster.block_rank();
     num_ranks = cluster.num_blocks();
-    first.seq = blockIdx.z;
+    first.seq = (args.seq_indices != nullptr) ? __ldg(args.seq_indices + blockIdx.z) : blockIdx.z;
     first.head_base = blockIdx.y * hpc;
     first.partition = 0;
     const uint32_t ctx = args.context_lens[first.seq];
@@ -957,14 +962,14 @@ template <int D>
 __global__ void __launch_bounds__(128)
 merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp_out,
                         const float *__restrict__ max_logits, const float *__restrict__ exp_sums,
-                        const uint32_t *__restrict__ context_lens, uint32_t num_heads,
-                        uint32_t max_num_partitions, uint32_t partition_size) {
+                        const uint32_t *__restrict__ context_lens, const uint32_t *__restrict__ seq_indices,
+                        uint32_t num_heads, uint32_t max_num_partitions, uint32_t partition_size) {
   constexpr uint32_t LANES_PER_ROW = D / 4;         // each lane owns 4 dims (8 bytes)
   constexpr uint32_t ROWS = 128 / LANES_PER_ROW;    // partitions handled in parallel
   constexpr uint32_t UNROLL = 4;                    // rows in flight per thread
   constexpr uint32_t WEIGHT_CACHE = 1024;           // weights kept in shared memory
   const uint32_t head = blockIdx.x;
-  const uint32_t seq = blockIdx.y;
+  const uint32_t seq = (seq_indices != nullptr) ? __ldg(seq_indices + blockIdx.y) : blockIdx.y;
   const uint32_t tid = threadIdx.x;
   // Launched with programmatic stream serialization, this grid may start while the attention
   // kernel drains; nothing is read before that kernel has completed and its writes are visible.
@@ -1065,16 +1070,19 @@ template <int D>
 __global__ void __launch_bounds__(128)
 merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict__ tmp_out,
                              const float *__restrict__ max_logits, const float *__restrict__ exp_sums,
-                             const uint32_t *__restrict__ context_lens, uint32_t num_heads,
+                             const uint32_t *__restrict__ context_lens,
+                             const uint32_t *__restrict__ seq_indices, uint32_t num_heads,
                              uint32_t num_pairs, uint32_t max_num_partitions, uint32_t partition_size) {
   constexpr uint32_t DPL = D / 32;          // dims per lane: 4 or 2
   constexpr uint32_t ROWS = 128 / (D / 4);  // residue classes of the CTA-per-pair kernel
   const uint32_t lane = threadIdx.x & 31u;
-  const uint32_t pair = blockIdx.x * 4 + (threadIdx.x >> 5); // seq * num_heads + head
+  const uint32_t work = blockIdx.x * 4 + (threadIdx.x >> 5); // (position in the launch) * num_heads + head
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (pair >= num_pairs) return;
-  const uint32_t seq = pair / num_heads;
+  if (work >= num_pairs) return;
+  const uint32_t pos = work / num_heads;
+  const uint32_t seq = (seq_indices != nullptr) ? __ldg(seq_indices + pos) : pos;
+  const uint32_t pair = seq * num_heads + (work - pos * num_heads); // seq * num_heads + head
   const uint32_t ctx = context_lens[seq];
   const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
   const size_t base = static_cast<size_t>(pair) * max_num_partitions;

@@ -103,6 +103,12 @@ typedef struct pa_params {
   const float *alibi_slopes;
   float softcap;
   float reserved2;
+  /* Optional subset launch (no reference counterpart): a device array of num_seqs sequence
+   * ids.  The call then processes exactly those sequences; every tensor is still indexed
+   * by the ids themselves (query[id], block_tables[id], out[id], scratch rows of id), so two
+   * calls with disjoint lists can share all buffers, e.g. a loop launch for the short and a
+   * reduce launch for the long sequences of one batch.  NULL = sequences 0 .. num_seqs-1. */
+  const uint32_t *seq_indices;
 } pa_params;
 
 /* Tiling knobs of include/paged_attention_policy_v2.hpp for one

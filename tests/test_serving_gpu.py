@@ -35,3 +35,29 @@ def test_auto_matches_oracle_and_single_variant_bits(cuda_device, kv):
     by_variant = {vname: run_entry(vname, c, dev)["out"] for vname in ("loop", "reduce")}
     for i, n in enumerate(ctx):
         assert torch.equal(out[i].cpu(), by_variant[choose_variant(n)][i]), f"sequence {i}"
+
+
+def test_decode_step_io_round_trip(cuda_device):
+    """Packed upload -> operator -> download gives the oracle's answer from host buffers."""
+    from flash_attention_factory_b200 import lib
+    from flash_attention_factory_b200.host_io import DecodeStepIO
+
+    ctx = [300, 45, 1025]
+    c = make_case(seed=62, num_seqs=3, num_heads=8, num_kv_heads=2, head_size=64, block_size=32,
+                  context_lens=ctx)
+    dev = cuda_device
+    io = DecodeStepIO(3, 8, 64, c["block_tables"].size(1), dev)
+    io.query_host.copy_(c["query"])
+    io.block_tables_host.copy_(c["block_tables"])
+    io.context_lens_host.copy_(c["context_lens"])
+    k, v = c["key_cache"].to(dev), c["value_cache"].to(dev)
+    ml = torch.empty(3, 8, 5, dtype=torch.float32, device=dev)
+    tmp = torch.empty(3, 8, 5, 64, dtype=torch.float16, device=dev)
+    io.upload()
+    lib.paged_attention_reduce.enqueue(ml, torch.empty_like(ml), tmp, io.out, torch.zeros(1, device=dev),
+                                       io.query, k, v, io.block_tables, io.context_lens, 4, c["sm_scale"],
+                                       32, max(ctx), torch.ones(8, device=dev), None, -1.0)
+    got = io.download().clone()
+    want = oracle.paged_attention_ref(c["query"], c["key_cache"], c["value_cache"], c["block_tables"],
+                                      c["context_lens"], sm_scale=c["sm_scale"])
+    assert_close(got, want, what="DecodeStepIO")
