@@ -180,6 +180,14 @@ AttnArgs make_attn_args(const pa_params *p) {
   a.block_shift = log2_pow2(p->block_size);
   // KV heads per CTA: with 4 a warp owns a head and nothing is merged across warps
   a.hpc = (p->num_kv_heads % 4 == 0) ? 4u : ((p->num_kv_heads % 2 == 0) ? 2u : 1u);
+  {
+    // debugging knob: PA_FORCE_HPC=1|2 lowers the number of KV heads per CTA
+    static const int forced = [] {
+      const char *e = std::getenv("PA_FORCE_HPC");
+      return e ? std::atoi(e) : 0;
+    }();
+    if ((forced == 1 || forced == 2) && static_cast<uint32_t>(forced) < a.hpc) a.hpc = forced;
+  }
   a.tokens_per_stage = policy::tokens_per_stage / a.hpc;
   a.rows_per_box = p->block_size < a.tokens_per_stage ? p->block_size : a.tokens_per_stage;
   a.boxes_per_stage = a.hpc * (a.tokens_per_stage / a.rows_per_box);
