@@ -160,7 +160,7 @@ inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_cou
 }
 
 template <int D, int KV>
-AttnArgs make_attn_args(const pa_params *p) {
+AttnArgs make_attn_args(const pa_params *p, bool loop_mode = false, int sm_count = 0) {
   using policy = paged_attention_policy_v2<D, KV>;
   AttnArgs a{};
   a.query = static_cast<const __half *>(p->query);
@@ -188,6 +188,13 @@ AttnArgs make_attn_args(const pa_params *p) {
     }();
     if ((forced == 1 || forced == 2) && static_cast<uint32_t>(forced) < a.hpc) a.hpc = forced;
   }
+  // The loop variant has one cluster of at most 8 CTAs per (sequence, head group): with very
+  // few sequences, fewer heads per CTA (warps then split the tokens of a head) is the only
+  // way to put a CTA on every SM
+  if (loop_mode)
+    while (a.hpc > 1 && static_cast<uint64_t>(p->num_seqs) * (p->num_kv_heads / a.hpc) * 8ull <
+                            static_cast<uint64_t>(sm_count))
+      a.hpc /= 2;
   a.tokens_per_stage = policy::tokens_per_stage / a.hpc;
   a.rows_per_box = p->block_size < a.tokens_per_stage ? p->block_size : a.tokens_per_stage;
   a.boxes_per_stage = a.hpc * (a.tokens_per_stage / a.rows_per_box);
@@ -216,7 +223,7 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
   if (int rc = get_device_info(&dev)) return rc;
   if (dev.cc_major < 10) return fail(PA_ERR_CUDA, "this library needs an sm_100a device");
 
-  AttnArgs args = make_attn_args<D, KV>(p);
+  AttnArgs args = make_attn_args<D, KV>(p, MODE == MODE_LOOP, dev.sm_count);
   if (MODE == MODE_SPLIT) {
     static std::atomic<uint32_t> next_slot{0}; // per kernel instantiation, like its counters
     args.sched_slot = next_slot.fetch_add(1, std::memory_order_relaxed) % kSchedSlots;
