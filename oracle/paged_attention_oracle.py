@@ -217,3 +217,38 @@ def reshape_and_cache_ref(key: torch.Tensor, value: torch.Tensor, key_cache: tor
             flat_k[slot] = (key[t].float() / fp8_scale).to(dt)
             flat_v[slot] = (value[t].float() / fp8_scale).to(dt)
     return kc, vc
+
+
+def paged_attention_ref_fp16(query, key_cache, value_cache, block_tables, context_lens,
+                             sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The reference's second oracle: the same attention in pure fp16 with reordered scaling
+    (`attention_ref(..., upcast=False, reorder_ops=True)`, test_paged.py:88-91,432-447).
+
+    Its error against the fp32 oracle is the yardstick of the reference's acceptance test:
+    max|out - ref| <= 3 * max|out_fp16 - ref| + 1e-5 (test_paged.py:603-604).
+    """
+    s, h, d = query.shape
+    out = torch.zeros(s, h, d, dtype=torch.float16)
+    for i in range(s):
+        n = int(context_lens[i])
+        if n == 0:
+            continue
+        k = gather_sequence(key_cache, block_tables[i], n).to(torch.float16)  # test_paged_fp8cache.py:80-81
+        v = gather_sequence(value_cache, block_tables[i], n).to(torch.float16)
+        g = h // k.shape[1]
+        k = k.repeat_interleave(g, dim=1)
+        v = v.repeat_interleave(g, dim=1)
+        scores = torch.einsum("hd,shd->hs", query[i], k / math.sqrt(d))  # reorder_ops: k is scaled
+        sf = scores.to(torch.float32)  # test_paged.py:112
+        smax = sf.max(dim=-1, keepdim=True).values
+        if sinks is not None:
+            sk = sinks.reshape(h, 1)
+            m = torch.maximum(sk, smax)
+            e = torch.exp(sf - m)
+            denom = e.sum(dim=-1, keepdim=True) + torch.exp(sk - m)
+        else:
+            e = torch.exp(sf - smax)
+            denom = e.sum(dim=-1, keepdim=True)
+        p = (e / denom).to(torch.float16)  # test_paged.py:119,123
+        out[i] = torch.einsum("hs,shd->hd", p, v)
+    return out

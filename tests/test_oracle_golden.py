@@ -58,3 +58,13 @@ def test_fp8_scale_is_applied_once():
     kd = (k8.to(torch.float16).float() * 0.5).half()  # 0.5 * x is exact in fp16
     b = oracle.paged_attention_ref(q, kd, kd, bt, [50])
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("name", golden_cases())
+def test_fp16_oracle_matches_reference_fp16_path(name):
+    """The pure-fp16 restatement is pinned to the reference's `out_pt` (upcast=False, reorder_ops=True)."""
+    c = load_golden(name)
+    pt = oracle.paged_attention_ref_fp16(c["query"], c["key_cache"], c["value_cache"], c["block_tables"],
+                                         c["context_lens"], sinks=c["sinks"])
+    err = (pt.float() - c["out_pt"].float()).abs()
+    assert (err <= 2.0 ** -10 * c["out_pt"].float().abs() + 1e-7).all(), err.max().item()
