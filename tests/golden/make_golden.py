@@ -2,7 +2,7 @@
 
 Run in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It loads the reference's two test files (test_paged.py, test_paged_fp8cache.py) with
 the missing ``lib`` extension package stubbed out, builds fixtures with the reference's
@@ -109,7 +109,9 @@ def make_case(ref16, ref8, name, fp8_dtype, batch, nheads, nheads_k, d, seqlen_k
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of baodii/flash_attention_factory>")
+    ref_root = Path(sys.argv[1])
     ref16 = load_reference_module(ref_root / "test_paged.py", "ref_test_paged")
     ref8 = load_reference_module(ref_root / "test_paged_fp8cache.py", "ref_test_paged_fp8cache")
     for case in CASES:
