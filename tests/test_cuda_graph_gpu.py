@@ -48,3 +48,31 @@ def test_enqueue_is_graph_capturable(cuda_device, variant, kv):
         torch.cuda.synchronize(dev)
         assert_close(out.cpu(), want, what=f"graph replay {variant}/{kv}")
     pkg.device_status()
+
+
+def test_torch_custom_ops(cuda_device):
+    """torch.ops.paged_attention_b200.* are registered and give the operators' results."""
+    import flash_attention_factory_b200.torch_ops  # noqa: F401  (registers the ops)
+
+    dev = cuda_device
+    ctx = [700, 33]
+    for kv, op in (("float16", "reduce"), ("float16", "loop"), ("float8_e5m2", "fp8_reduce"),
+                   ("float8_e5m2", "fp8_loop")):
+        c = make_case(seed=83, num_seqs=2, num_heads=8, num_kv_heads=2, head_size=128, block_size=16,
+                      context_lens=ctx, kv_dtype=kv)
+        q, k, v = c["query"].to(dev), c["key_cache"].to(dev), c["value_cache"].to(dev)
+        bt, cl = c["block_tables"].to(dev), c["context_lens"].to(dev)
+        ml = torch.empty(2, 8, 2, dtype=torch.float32, device=dev)
+        es = torch.empty_like(ml)
+        tmp = torch.empty(2, 8, 2, 128, dtype=torch.float16, device=dev)
+        out = torch.zeros(2, 8, 128, dtype=torch.float16, device=dev)
+        alibi = torch.ones(8, dtype=torch.float32, device=dev)
+        fn = getattr(torch.ops.paged_attention_b200, op)
+        if op.startswith("fp8"):
+            fn(ml, es, tmp, out, q, k, v, bt, cl, 4, c["sm_scale"], 1.0, 16, max(ctx), alibi, None, -1.0)
+        else:
+            fn(ml, es, tmp, out, q, k, v, bt, cl, 4, c["sm_scale"], 16, max(ctx), alibi, None, -1.0)
+        torch.cuda.synchronize(dev)
+        want = oracle.paged_attention_ref(c["query"], c["key_cache"], c["value_cache"], c["block_tables"],
+                                          c["context_lens"], sm_scale=c["sm_scale"])
+        assert_close(out.cpu(), want, what=f"torch op {op}")
