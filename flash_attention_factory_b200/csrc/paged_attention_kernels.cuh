@@ -896,12 +896,13 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       const bool ok = (*abort_flag == 0u);
       const uint32_t ctid = threadIdx.x - 32;
       const uint32_t slices = NW / hpc;
-      const uint32_t dims_per_rank = D / num_ranks; // cluster sizes are powers of two <= 8
+      // each CTA of the cluster writes the dims d with d mod num_ranks == its rank
+      const uint32_t dims_per_rank = (D - cta_rank + num_ranks - 1) / num_ranks;
       float *areas = reinterpret_cast<float *>(smem);
       for (uint32_t idx = ctid; idx < hpc * 8 * dims_per_rank; idx += NCONS) {
         const uint32_t hh = idx / (8 * dims_per_rank);
         const uint32_t g = (idx / dims_per_rank) % 8;
-        const uint32_t d = cta_rank * dims_per_rank + idx % dims_per_rank;
+        const uint32_t d = cta_rank + (idx % dims_per_rank) * num_ranks;
         float m_all = neg_infinity();
         for (uint32_t r = 0; r < num_ranks; ++r) {
           const float *peer = cluster.map_shared_rank(areas, r);
