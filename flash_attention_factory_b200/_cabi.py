@@ -35,6 +35,7 @@ EXPORTED_SYMBOLS = (
     "pa_partition_size",
     "pa_last_error",
     "pa_device_status",
+    "pa_selftest_wait_timeout",
     "pa_version",
 )
 
@@ -148,6 +149,8 @@ def load_library() -> ctypes.CDLL:
     lib.pa_last_error.restype = ctypes.c_char_p
     lib.pa_device_status.argtypes = []
     lib.pa_device_status.restype = ctypes.c_int
+    lib.pa_selftest_wait_timeout.argtypes = [ctypes.c_uint32]
+    lib.pa_selftest_wait_timeout.restype = ctypes.c_int
     lib.pa_version.argtypes = []
     lib.pa_version.restype = ctypes.c_char_p
     _lib = lib

@@ -53,6 +53,26 @@ int get_device_info(DeviceInfo *info) {
   return PA_OK;
 }
 
+// Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever completes.
+// The wait has to give up after `limit_ns`, raise the CTA's abort flag and leave the kernel
+// through the normal exit, which records the time-out in the device status word.
+__global__ void selftest_wait_kernel(unsigned long long limit_ns, int *gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0u;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const bool ok = mbar_wait_bounded(&bar, 0u, &abort_flag, limit_ns); // nobody arrives
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *gave_up = ok ? 0 : 1;
+    if (abort_flag != 0u) atomicExch(&g_pa_device_status, 4);
+  }
+}
+
 int read_status_loop(int *v);
 int read_status_reduce(int *v);
 int read_status_fp8_loop(int *v);
@@ -99,11 +119,29 @@ PA_API int pa_query_policy(uint32_t head_size, uint32_t block_size, uint32_t gro
   return PA_OK;
 }
 
+PA_API int pa_selftest_wait_timeout(uint32_t limit_us) {
+  if (limit_us == 0 || limit_us > 500000u) return pa::fail(PA_ERR_BAD_ARG, "limit_us must be in 1..500000");
+  int *flag = nullptr;
+  cudaError_t err = cudaMalloc(&flag, sizeof(int));
+  if (err != cudaSuccess) return pa::fail(PA_ERR_CUDA, "cudaMalloc failed: %s", cudaGetErrorString(err));
+  err = cudaMemset(flag, 0xff, sizeof(int));
+  if (err == cudaSuccess) {
+    pa::selftest_wait_kernel<<<1, 64>>>(static_cast<unsigned long long>(limit_us) * 1000ull, flag);
+    err = cudaDeviceSynchronize();
+  }
+  int gave_up = -1;
+  if (err == cudaSuccess) err = cudaMemcpy(&gave_up, flag, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaFree(flag);
+  if (err != cudaSuccess) return pa::fail(PA_ERR_CUDA, "self-test failed: %s", cudaGetErrorString(err));
+  if (gave_up != 1) return pa::fail(PA_ERR_CUDA, "the bounded wait did not give up (flag %d)", gave_up);
+  return PA_OK;
+}
+
 PA_API int pa_device_status(void) {
   cudaError_t err = cudaDeviceSynchronize();
   if (err != cudaSuccess) return pa::fail(PA_ERR_CUDA, "cudaDeviceSynchronize failed: %s", cudaGetErrorString(err));
-  int (*readers[4])(int *) = {pa::read_status_loop, pa::read_status_reduce, pa::read_status_fp8_loop,
-                              pa::read_status_fp8_reduce};
+  int (*readers[5])(int *) = {pa::read_status_loop, pa::read_status_reduce, pa::read_status_fp8_loop,
+                              pa::read_status_fp8_reduce, pa::read_and_clear_device_status};
   int worst = 0;
   for (auto reader : readers) {
     int v = 0;

@@ -231,6 +231,13 @@ PA_API const char *pa_last_error(void);
  * Synchronises the device. */
 PA_API int pa_device_status(void);
 
+/* Self-test of the failure path (test hook; allocates 4 bytes of device memory and
+ * synchronises): launches one CTA that waits on a barrier nothing ever completes, with the
+ * given limit.  Returns PA_OK if the wait gave up within the limit; afterwards
+ * pa_device_status() reports PA_ERR_TIMEOUT once, exactly as it would after a real
+ * time-out in an attention kernel. */
+PA_API int pa_selftest_wait_timeout(uint32_t limit_us);
+
 /* Library version, "major.minor". */
 PA_API const char *pa_version(void);
 

@@ -189,14 +189,15 @@ PA_DEV uint64_t global_timer_ns() {
 // Waits for a phase of `bar` with a time limit.  Returns false if the limit
 // (about one second) passed or another warp of the CTA already gave up
 // (*abort_flag != 0); the caller then leaves its loop instead of spinning on.
-PA_DEV bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
+PA_DEV bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag,
+                              uint64_t limit_ns = 1000000000ull) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 0x3ffu) == 0u) {
       if (*abort_flag != 0u) return false;
-      if (global_timer_ns() - t0 > 1000000000ull) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1u;
         return false;
       }
