@@ -147,11 +147,6 @@ inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_cou
   uint32_t cs = 1;
   while (cs < 8 && units * cs < want) cs *= 2;
   if (p->max_context_len != 0) {
-    // Long contexts mean long-lived CTAs and, when the batch is ragged, a long tail behind the
-    // longest sequence: split one step further (measured on B200: ragged 1k-8k contexts run
-    // 5 % faster with 4 CTAs than with 2, log-normal contexts up to 32k 25 % faster with 2
-    // than with 1, uniform 4k contexts are fastest unsplit).
-    if (p->max_context_len >= 8192 && cs < 8) cs *= 2;
     // a CTA should own at least 8 stages of the longest context: below that the cluster merge
     // and the extra launches cost more than the split saves (config 1: 24 us unsplit, 36 us
     // with 8 CTAs per cluster)
@@ -264,6 +259,9 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
     // portable cluster sizes only: 9..16 CTAs per cluster measured 30-40 % slower on B200
     // (fewer clusters fit a GPC at once)
     const uint32_t cs = choose_cluster_size(p, args.hpc, dev.sm_count, args.tokens_per_stage);
+    // the order in which clusters start only matters when they do not all fit at once
+    const uint64_t ctas = static_cast<uint64_t>(cs) * (p->num_kv_heads / args.hpc) * p->num_seqs;
+    args.longest_first_hint = (ctas > 2ull * static_cast<uint64_t>(dev.sm_count)) ? p->max_context_len : 0u;
     cfg.gridDim = dim3(cs, p->num_kv_heads / args.hpc, p->num_seqs);
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = cs;

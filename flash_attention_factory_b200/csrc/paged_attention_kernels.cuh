@@ -86,6 +86,8 @@ struct AttnArgs {
   // optional list of the sequences this launch covers (num_seqs entries); all tensors are
   // still indexed by the sequence ids found in the list
   const uint32_t *seq_indices;
+  // loop mode: context-length hint used to launch long sequences first (0 = keep the order)
+  uint32_t longest_first_hint;
   // opt-in score modifiers (off in the reference, whose call sites are commented out,
   // paged_attention_kernel_loop.hpp:329-342): soft-cap s -> cap * tanh(s / cap), then an ALiBi
   // bias slope[h] * (t - (ctx - 1)) on the score of token t
@@ -305,7 +307,47 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     cg::cluster_group cluster = cg::this_cluster();
     cta_rank = cluster.block_rank();
     num_ranks = cluster.num_blocks();
-    first.seq = (args.seq_indices != nullptr) ? __ldg(args.seq_indices + blockIdx.z) : blockIdx.z;
+    // Clusters start in block-index order.  With ragged lengths a long sequence that starts
+    // last leaves the machine idle behind it, so block index z is mapped to the z-th sequence
+    // in (approximately) descending length: 16 length classes, longest class first, position
+    // order inside a class.  Every CTA computes the same map from the context lengths alone.
+    uint32_t position = blockIdx.z;
+    if (args.longest_first_hint != 0u && args.num_seqs > 1u) {
+      __shared__ uint32_t class_count[16];
+      __shared__ uint32_t chosen;
+      if (threadIdx.x < 16) class_count[threadIdx.x] = 0u;
+      __syncthreads();
+      auto length_class = [&](uint32_t pos) -> uint32_t {
+        const uint32_t id = (args.seq_indices != nullptr) ? __ldg(args.seq_indices + pos) : pos;
+        const uint64_t c = __ldg(args.context_lens + id);
+        const uint64_t k = c * 16ull / (static_cast<uint64_t>(args.longest_first_hint) + 1ull);
+        return 15u - static_cast<uint32_t>(k > 15ull ? 15ull : k); // class 0 = longest
+      };
+      for (uint32_t pos = threadIdx.x; pos < args.num_seqs; pos += blockDim.x)
+        atomicAdd(&class_count[length_class(pos)], 1u);
+      __syncthreads();
+      if (warp == 0) {
+        uint32_t want = blockIdx.z, cls = 0;
+        while (cls < 15u && want >= class_count[cls]) want -= class_count[cls++];
+        // the want-th sequence (in position order) of class cls
+        uint32_t found = blockIdx.z;
+        for (uint32_t base = 0; base < args.num_seqs; base += 32) {
+          const uint32_t pos = base + lane;
+          const bool hit = pos < args.num_seqs && length_class(pos) == cls;
+          const uint32_t mask = __ballot_sync(0xffffffffu, hit);
+          const uint32_t n = __popc(mask);
+          if (want < n) {
+            found = base + __fns(mask, 0, want + 1);
+            break;
+          }
+          want -= n;
+        }
+        if (lane == 0) chosen = found;
+      }
+      __syncthreads();
+      position = chosen;
+    }
+    first.seq = (args.seq_indices != nullptr) ? __ldg(args.seq_indices + position) : position;
     first.head_base = blockIdx.y * hpc;
     first.partition = 0;
     const uint32_t ctx = args.context_lens[first.seq];
