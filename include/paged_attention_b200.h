@@ -119,7 +119,7 @@ typedef struct pa_policy_info {
   uint32_t head_size_stride;      /* reference MMA k-slice (16) */
   uint32_t partition_stride;      /* merge kernel: partitions per step (8) */
   uint32_t max_partitions_per_sg; /* reference merge-kernel register rows */
-  uint32_t tokens_per_stage;      /* this library: tokens per shared-memory ring stage */
+  uint32_t tokens_per_stage;      /* this library: rows (KV heads x tokens) per shared-memory ring stage */
   uint32_t ring_stages;           /* this library: TMA ring depth for the fp16 cache */
   uint32_t ring_stages_fp8;       /* this library: TMA ring depth for an FP8 cache */
   uint32_t consumer_warps;        /* MMA warps per CTA (one more warp issues TMA) */

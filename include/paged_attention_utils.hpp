@@ -207,15 +207,6 @@ PA_DEV bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, volatile uint32_t 
 }
 
 // ------------------------------------------------------------------------ TMA
-// Tiled 2-D copy global -> this CTA's shared memory, completion on `bar`.
-PA_DEV void tma_load_2d(uint32_t dst_smem, const void *tensor_map, uint64_t *bar, int32_t x,
-                        int32_t y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst_smem),
-      "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
 // L2 policy for data that is read exactly once (the KV stream): evict it first
 PA_DEV uint64_t l2_evict_first_policy() {
   uint64_t policy;
