@@ -470,6 +470,20 @@ def main() -> None:
 
     pkg.device_status()
 
+    # ---- read rate of a kernel that only reads, same pools, one launch, this GPU, this run
+    read_gbs, bulk_gbs, read_bytes = None, None, 0
+    if rank == 0:
+        from flash_attention_factory_b200 import _cabi
+
+        kp, vp = w.k[0], w.v[0]
+        read_bytes = (kp.numel() + vp.numel()) * kp.element_size()
+        if read_bytes >= 4 * L2_BYTES:  # several times L2, else the figure is not an HBM figure
+            cur = torch.cuda.current_stream(device).cuda_stream
+            read_gbs = _cabi.measure_read_bandwidth(kp.data_ptr(), read_bytes // 2, 10, cur,
+                                                    vp.data_ptr(), read_bytes // 2, method=0)
+            bulk_gbs = _cabi.measure_read_bandwidth(kp.data_ptr(), read_bytes // 2, 10, cur,
+                                                    vp.data_ptr(), read_bytes // 2, method=1)
+
     # ---- max over ranks, whole-job aggregate
     stats = torch.tensor([ms_total, ms_e2e, statistics.mean(attn_us)], dtype=torch.float64, device=device)
     total_bytes = torch.tensor([float(w.kv_bytes)], dtype=torch.float64, device=device)
@@ -497,6 +511,10 @@ def main() -> None:
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
                          "frac_of_8TBps": round(achieved / NOMINAL_HBM_GBS, 4),
+                         "read_only_stream_gbs": round(read_gbs, 1) if read_gbs else None,
+                         "read_only_bulk_copy_gbs": round(bulk_gbs, 1) if bulk_gbs else None,
+                         "read_only_stream_bytes": read_bytes if read_gbs else None,
+                         "frac_of_read_only_stream": round(achieved / max(read_gbs, bulk_gbs), 4) if read_gbs else None,
                          "kernel_us": round(attn_mean_us, 2),
                          "merge_kernel_us": round(statistics.mean(merge_us), 2) if merge_us else None,
                          "traffic": TRAFFIC_BYTES.get((a.config, variant)) if not overridden else None},

@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "pa_last_error",
     "pa_device_status",
     "pa_selftest_wait_timeout",
+    "pa_measure_read_bandwidth",
     "pa_version",
 )
 
@@ -151,6 +152,10 @@ def load_library() -> ctypes.CDLL:
     lib.pa_device_status.restype = ctypes.c_int
     lib.pa_selftest_wait_timeout.argtypes = [ctypes.c_uint32]
     lib.pa_selftest_wait_timeout.restype = ctypes.c_int
+    lib.pa_measure_read_bandwidth.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_uint64,
+                                              ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
+                                              ctypes.POINTER(ctypes.c_float)]
+    lib.pa_measure_read_bandwidth.restype = ctypes.c_int
     lib.pa_version.argtypes = []
     lib.pa_version.restype = ctypes.c_char_p
     _lib = lib
@@ -184,6 +189,17 @@ def partition_size(head_size: int) -> int:
 def device_status() -> None:
     """Synchronises the current device and raises if a kernel gave up a bounded wait."""
     check(load_library().pa_device_status())
+
+
+def measure_read_bandwidth(ptr: int, nbytes: int, iters: int = 10, stream: int = 0,
+                           ptr2: int = 0, nbytes2: int = 0, method: int = 0) -> float:
+    """GB/s of a kernel that only reads `nbytes` at `ptr` (+ `nbytes2` at `ptr2`), blocking.
+    method 0: 16-byte loads; method 1: bulk copies into a shared-memory ring."""
+    rate = ctypes.c_float(0.0)
+    check(load_library().pa_measure_read_bandwidth(ctypes.c_void_p(ptr), nbytes, ctypes.c_void_p(ptr2 or None),
+                                                   nbytes2, method, iters, ctypes.c_void_p(stream),
+                                                   ctypes.byref(rate)))
+    return float(rate.value)
 
 
 def launch(entry: str, params: PaParams, stream: int, timed: bool) -> list[float]:

@@ -1185,18 +1185,27 @@ merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict_
     const float w = __shfl_sync(0xffffffffu, w_lane, u) * inv_w;
     if (u < np) add_row(u % ROWS, pre[u], w);
   }
-  for (uint32_t p0 = PREFETCH; p0 < np; p0 += ROWS) {
+  // the rest in groups of PREFETCH partitions: all rows and statistics of a group are requested
+  // before the first is used (a long sequence is a chain of such groups, so the depth of a
+  // group sets its latency); within a residue class the partitions still add in increasing order
+  for (uint32_t p0 = PREFETCH; p0 < np; p0 += PREFETCH) {
+    float ml[PREFETCH], es[PREFETCH];
 #pragma unroll
-    for (uint32_t r = 0; r < ROWS; ++r) {
-      const uint32_t p = p0 + r;
+    for (uint32_t u = 0; u < PREFETCH; ++u) {
+      const uint32_t p = p0 + u;
+      pre[u] = make_uint2(0u, 0u);
+      ml[u] = neg_infinity();
+      es[u] = 0.f;
       if (p < np) {
-        const float w = exp_sums[base + p] * __expf(max_logits[base + p] - m) * inv_w;
-        uint2 raw = make_uint2(0u, 0u);
-        if constexpr (DPL == 4) raw = __ldg(reinterpret_cast<const uint2 *>(rows + static_cast<size_t>(p) * D));
-        else raw.x = __ldg(reinterpret_cast<const uint32_t *>(rows + static_cast<size_t>(p) * D));
-        add_row(r, raw, w);
+        if constexpr (DPL == 4) pre[u] = __ldg(reinterpret_cast<const uint2 *>(rows + static_cast<size_t>(p) * D));
+        else pre[u].x = __ldg(reinterpret_cast<const uint32_t *>(rows + static_cast<size_t>(p) * D));
+        ml[u] = max_logits[base + p];
+        es[u] = exp_sums[base + p];
       }
     }
+#pragma unroll
+    for (uint32_t u = 0; u < PREFETCH; ++u)
+      if (p0 + u < np) add_row(u % ROWS, pre[u], es[u] * __expf(ml[u] - m) * inv_w);
   }
   float total[DPL];
 #pragma unroll

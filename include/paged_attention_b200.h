@@ -238,6 +238,18 @@ PA_API int pa_device_status(void);
  * time-out in an attention kernel. */
 PA_API int pa_selftest_wait_timeout(uint32_t limit_us);
 
+/* Measurement aid, no counterpart in the reference: times `iters` launches of a kernel that
+ * only reads, with CUDA events on `stream`, and stores the read rate in GB/s.  One launch reads
+ * `bytes` at `buf` and then, if `buf2` is not NULL, `bytes2` at `buf2` (both 16-byte aligned)
+ * -- e.g. the K pool and the V pool, so that the figure is for the same byte count in one
+ * launch as the attention kernel reads.  method 0: 16-byte loads with a grid stride, folded
+ * into a checksum; method 1: 16 KB bulk copies into a shared-memory ring (the copy engine the
+ * attention kernels use), data never looked at, whole 16 KB chunks only.  Blocks until done;
+ * allocates 4 bytes of device memory.  With buffers much larger than L2 this is the HBM read
+ * rate a kernel that does nothing but read reaches at that size. */
+PA_API int pa_measure_read_bandwidth(const void *buf, uint64_t bytes, const void *buf2, uint64_t bytes2,
+                                     uint32_t method, uint32_t iters, void *stream, float *gb_per_s);
+
 /* Library version, "major.minor". */
 PA_API const char *pa_version(void);
 

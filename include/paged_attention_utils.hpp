@@ -224,6 +224,15 @@ PA_DEV void tma_load_3d(uint32_t dst_smem, const void *tensor_map, uint64_t *bar
       "l"(l2_policy)
       : "memory");
 }
+// Untiled bulk copy global -> this CTA's shared memory (both addresses 16-byte aligned, size
+// a multiple of 16 bytes), completion on `bar`.
+PA_DEV void bulk_load_1d(uint32_t dst_smem, const void *src, uint32_t bytes, uint64_t *bar, uint64_t l2_policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      :: "r"(dst_smem), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(l2_policy)
+      : "memory");
+}
+
 PA_DEV void tma_prefetch_descriptor(const void *tensor_map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensor_map)) : "memory");
 }
