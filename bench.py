@@ -92,6 +92,8 @@ class Workload:
         gc = torch.Generator().manual_seed(seed)
         # block tables: a random permutation of the physical blocks, cut into rows
         perm = torch.randperm(num_blocks, generator=gc).to(torch.int32)
+        if spec.get("block_order") == "sequential":
+            perm = torch.arange(num_blocks, dtype=torch.int32)
         bt = torch.zeros(s, mb, dtype=torch.int32)
         pos = 0
         for i, nb in enumerate(blocks_needed):
@@ -312,6 +314,7 @@ def describe_config(a, spec: dict, variant: str, world: int, ctx) -> dict:
         "kv_bytes_per_call_per_gpu": kv_bytes, "cache_copies_rotated": copies,
         "l2_policy": "inputs larger than L2" if copies == 1 else
                      f"rotating over {copies} cache copies (> 4x L2 in total)",
+        "block_order": spec.get("block_order", "random"),
         "launch": "cuda graph replay" if getattr(a, "cuda_graph", False) else "direct",
         "sharding": "none" if world == 1 else
                     ("sequences split by cumulative KV length" if strong else "one shard per GPU"),
@@ -343,6 +346,11 @@ def main() -> None:
     ap.add_argument("--heads", type=int, default=None, help="override the number of query heads")
     ap.add_argument("--kv-heads", type=int, default=None, help="override the number of KV heads")
     ap.add_argument("--block-size", type=int, default=None, choices=[16, 32, 64, 128])
+    ap.add_argument("--e2e-mode", default="step", choices=["torch", "step", "direct"],
+                    help="end-to-end leg: torch copies + enqueue, one pa_decode_step_host call per step, "
+                         "or the same with the kernels writing the result into pinned host memory")
+    ap.add_argument("--block-order", default=None, choices=["random", "sequential"],
+                    help="physical placement of a sequence's blocks (default: a random permutation)")
     ap.add_argument("--num-seqs", type=int, default=None,
                     help="override the number of sequences (small cases for profiler captures)")
     a = ap.parse_args()
@@ -364,7 +372,9 @@ def main() -> None:
                      ("block_size", a.block_size)):
         if val is not None:
             spec[key] = val
-    overridden = any(v is not None for v in (a.num_seqs, a.kv, a.head_size, a.heads, a.kv_heads, a.block_size))
+    if a.block_order is not None:
+        spec["block_order"] = a.block_order
+    overridden = any(v is not None for v in (a.num_seqs, a.kv, a.head_size, a.heads, a.kv_heads, a.block_size, a.block_order))
     variant = a.variant or pick_variant(spec)
 
     if a.impl == "reference":
@@ -447,7 +457,16 @@ def main() -> None:
     out_resident = w.out
     w.out = io.out  # the step writes into the buffer that is downloaded
 
+    bound = None
+    if variant != "auto" and a.e2e_mode != "torch":
+        # one library call per step: upload, launch, download, wait (pa_decode_step_host)
+        bound = [io.bind(w.module().ENTRY, w.module().params(*w.args(i, io.query, io.block_tables, io.context_lens)),
+                         direct_out=(a.e2e_mode == "direct")) for i in range(w.copies)]
+
     def e2e_step(i):
+        if bound is not None:
+            bound[i % w.copies].run()
+            return
         io.upload()  # query + block tables + context lengths: one copy from pinned memory
         w.enqueue(i, io.query, io.block_tables, io.context_lens)
         io.download()  # the caller reads the result now

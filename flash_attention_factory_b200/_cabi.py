@@ -37,6 +37,7 @@ EXPORTED_SYMBOLS = (
     "pa_device_status",
     "pa_selftest_wait_timeout",
     "pa_measure_read_bandwidth",
+    "pa_decode_step_host",
     "pa_version",
 )
 
@@ -115,6 +116,22 @@ class PaCacheWriteParams(ctypes.Structure):
     ]
 
 
+class PaHostStep(ctypes.Structure):
+    """struct pa_host_step of include/paged_attention_b200.h."""
+
+    _fields_ = [
+        ("host_in", ctypes.c_void_p),
+        ("dev_in", ctypes.c_void_p),
+        ("in_bytes", ctypes.c_uint64),
+        ("host_out", ctypes.c_void_p),
+        ("out_bytes", ctypes.c_uint64),
+    ]
+
+
+ENTRY_IDS = {"launch_kernels_loop": 0, "launch_kernels_reduce": 1, "launch_kernels_fp8_loop": 2,
+             "launch_kernels_fp8_reduce": 3}
+
+
 def library_path() -> Path:
     return Path(__file__).resolve().parent / _LIB_NAME
 
@@ -156,6 +173,9 @@ def load_library() -> ctypes.CDLL:
                                               ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
                                               ctypes.POINTER(ctypes.c_float)]
     lib.pa_measure_read_bandwidth.restype = ctypes.c_int
+    lib.pa_decode_step_host.argtypes = [ctypes.c_int32, ctypes.POINTER(PaParams), ctypes.POINTER(PaHostStep),
+                                        ctypes.c_void_p, ctypes.c_int32]
+    lib.pa_decode_step_host.restype = ctypes.c_int
     lib.pa_version.argtypes = []
     lib.pa_version.restype = ctypes.c_char_p
     _lib = lib

@@ -5,10 +5,20 @@ result is one [S, H, D] fp16 tensor.  Copying them as three separate tensors cos
 transfer latencies; `DecodeStepIO` keeps them in one pinned staging buffer with a device
 mirror, so a step is one H2D copy, the kernel launches, one D2H copy and a stream wait.
 The KV cache is not part of it: it is state that stays on the device.
+
+`bind()` returns a `BoundStep` whose `run()` does the whole step as one call into the library (`pa_decode_step_host`):
+the argument block is built once, so a step costs one ctypes call instead of tensor checks
+and three torch calls.  With `direct_out=True` the kernels write the result straight into the
+pinned host buffer (pinned memory is device-visible under unified addressing), which removes
+the download copy from the critical path.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
+
+from . import _cabi
 
 
 def _round_up(n: int, a: int) -> int:
@@ -52,3 +62,42 @@ class DecodeStepIO:
         self.out_host.copy_(self.out, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         return self.out_host
+
+    def bind(self, entry: str, params: "_cabi.PaParams", direct_out: bool = False) -> "BoundStep":
+        """Fixes the entry point and its argument block; `BoundStep.run()` then is one step.
+
+        `params` is what `lib.<module>.params(...)` returned for tensors that include this
+        object's `query`, `block_tables`, `context_lens` and `out`; it is copied, and with
+        `direct_out` its `out` pointer is redirected to the pinned host buffer."""
+        return BoundStep(self, entry, params, direct_out)
+
+
+class BoundStep:
+    """One decode step on fixed tensors as a single library call (`pa_decode_step_host`)."""
+
+    def __init__(self, io: DecodeStepIO, entry: str, params: "_cabi.PaParams", direct_out: bool):
+        self.io = io
+        self.entry = _cabi.ENTRY_IDS[entry]
+        self.params = _cabi.PaParams()
+        ctypes.memmove(ctypes.byref(self.params), ctypes.byref(params), ctypes.sizeof(_cabi.PaParams))
+        self.host_step = _cabi.PaHostStep()
+        self.host_step.host_in = io.host.data_ptr()
+        self.host_step.dev_in = io.dev.data_ptr()
+        self.host_step.in_bytes = io.h2d_bytes
+        if direct_out:
+            self.params.out = io.out_host.data_ptr()
+            self.host_step.host_out = None
+            self.host_step.out_bytes = 0
+        else:
+            self.host_step.host_out = io.out_host.data_ptr()
+            self.host_step.out_bytes = io.d2h_bytes
+        self._fn = _cabi.load_library().pa_decode_step_host
+
+    def run(self, synchronize: bool = True) -> torch.Tensor:
+        """Upload, launch, download (and wait) on the current stream; returns the host result."""
+        stream = torch.cuda.current_stream(self.io.device).cuda_stream
+        rc = self._fn(self.entry, ctypes.byref(self.params), ctypes.byref(self.host_step),
+                      ctypes.c_void_p(stream), 1 if synchronize else 0)
+        if rc != _cabi.PA_OK:
+            _cabi.check(rc)
+        return self.io.out_host

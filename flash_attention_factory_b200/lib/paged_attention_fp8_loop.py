@@ -10,7 +10,7 @@ from __future__ import annotations
 
 from . import _shim
 
-_ENTRY = "launch_kernels_fp8_loop"
+ENTRY = _ENTRY = "launch_kernels_fp8_loop"
 
 
 def run(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
@@ -23,6 +23,20 @@ def run(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache
     return _shim.run_entry(_ENTRY, p, query.device)
 
 
+def params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
+           block_tables, context_lens, num_queries_per_tokens, sm_scale, fp8_scale, block_size,
+           max_context_len, alibi_slopes, sinks, softcap, *, k_scale_per_head=None, v_scale_per_head=None,
+           use_alibi=False, use_softcap=False):
+    """The checked argument block (`pa_params`) of an ``enqueue`` call with these arguments,
+    for callers that launch many steps on the same tensors (`host_io.DecodeStepIO.bind`)."""
+    p = _shim.build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
+                           value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
+                           fp8_scale, block_size, max_context_len, alibi_slopes, sinks, softcap,
+                           fp8=True, k_scale_per_head=k_scale_per_head, v_scale_per_head=v_scale_per_head,
+                           use_alibi=use_alibi, use_softcap=use_softcap)
+    return p
+
+
 def enqueue(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
             block_tables, context_lens, num_queries_per_tokens, sm_scale, fp8_scale, block_size,
             max_context_len, alibi_slopes, sinks, softcap, *, k_scale_per_head=None, v_scale_per_head=None,
@@ -31,9 +45,8 @@ def enqueue(max_logits, exp_sums, tem_output, output, debug_output, query, key_c
 
     ``k_scale_per_head`` / ``v_scale_per_head`` (float32 [num_kv_heads], optional, no reference
     counterpart) replace the scalar ``fp8_scale`` for K / V with one scale per KV head."""
-    p = _shim.build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
-                           value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
-                           fp8_scale, block_size, max_context_len, alibi_slopes, sinks, softcap,
-                           fp8=True, k_scale_per_head=k_scale_per_head, v_scale_per_head=v_scale_per_head,
-                           use_alibi=use_alibi, use_softcap=use_softcap)
+    p = params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
+               block_tables, context_lens, num_queries_per_tokens, sm_scale, fp8_scale, block_size,
+               max_context_len, alibi_slopes, sinks, softcap, k_scale_per_head=k_scale_per_head,
+               v_scale_per_head=v_scale_per_head, use_alibi=use_alibi, use_softcap=use_softcap)
     _shim.enqueue_entry(_ENTRY, p, query.device)

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from . import _shim
 
-_ENTRY = "launch_kernels_loop"
+ENTRY = _ENTRY = "launch_kernels_loop"
 
 
 def run(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
@@ -20,6 +20,18 @@ def run(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache
     return _shim.run_entry(_ENTRY, p, query.device)
 
 
+def params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
+           block_tables, context_lens, num_queries_per_tokens, sm_scale, block_size,
+           max_context_len, alibi_slopes, sinks, softcap, *, use_alibi=False, use_softcap=False):
+    """The checked argument block (`pa_params`) of an ``enqueue`` call with these arguments,
+    for callers that launch many steps on the same tensors (`host_io.DecodeStepIO.bind`)."""
+    p = _shim.build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
+                           value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
+                           1.0, block_size, max_context_len, alibi_slopes, sinks, softcap, fp8=False,
+                           use_alibi=use_alibi, use_softcap=use_softcap)
+    return p
+
+
 def enqueue(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
             block_tables, context_lens, num_queries_per_tokens, sm_scale, block_size,
             max_context_len, alibi_slopes, sinks, softcap, *, use_alibi=False, use_softcap=False):
@@ -27,8 +39,7 @@ def enqueue(max_logits, exp_sums, tem_output, output, debug_output, query, key_c
 
     ``use_alibi`` / ``use_softcap`` (no reference counterpart) make ``alibi_slopes`` / ``softcap``
     live; by default both are ignored, as the reference ignores them."""
-    p = _shim.build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
-                           value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
-                           1.0, block_size, max_context_len, alibi_slopes, sinks, softcap, fp8=False,
-                           use_alibi=use_alibi, use_softcap=use_softcap)
+    p = params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
+               block_tables, context_lens, num_queries_per_tokens, sm_scale, block_size, max_context_len,
+               alibi_slopes, sinks, softcap, use_alibi=use_alibi, use_softcap=use_softcap)
     _shim.enqueue_entry(_ENTRY, p, query.device)

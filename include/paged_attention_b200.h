@@ -189,6 +189,33 @@ PA_API int launch_kernels_fp8_reduce(const pa_params *p, void *stream, float *us
  * array needs clearing between calls. */
 PA_API int launch_kernels_reduce_static_scratch(const pa_params *p, void *stream);
 
+/* Host side of one decode step, for callers whose per-step inputs live in host memory. */
+typedef struct pa_host_step {
+  const void *host_in; /* pinned host staging buffer: whatever per-step inputs pa_params reads
+                          (query, block tables, context lengths), packed by the caller */
+  void *dev_in;        /* its device mirror; the pa_params pointers point into this buffer */
+  uint64_t in_bytes;   /* bytes copied host_in -> dev_in before the launch (0: no upload) */
+  void *host_out;      /* pinned host buffer that receives pa_params.out after the launch */
+  uint64_t out_bytes;  /* bytes copied pa_params.out -> host_out (0: no download, e.g. because
+                          pa_params.out already is device-visible pinned host memory and the
+                          kernel writes the result there itself) */
+} pa_host_step;
+
+typedef enum pa_entry {
+  PA_ENTRY_LOOP = 0,
+  PA_ENTRY_REDUCE = 1,
+  PA_ENTRY_FP8_LOOP = 2,
+  PA_ENTRY_FP8_REDUCE = 3
+} pa_entry;
+
+/* One decode step with host buffers, in one call (no counterpart in the reference, whose
+ * bindings take device tensors): upload of the step's inputs, the asynchronous form of the
+ * chosen entry point, download of the result, all on `stream`; if `synchronize` is non-zero
+ * the call returns after the stream has drained, i.e. when host_out (or the host memory behind
+ * pa_params.out) holds the result.  Allocates nothing. */
+PA_API int pa_decode_step_host(int32_t entry, const pa_params *p, const pa_host_step *io, void *stream,
+                               int32_t synchronize);
+
 /* Arguments of pa_reshape_and_cache. */
 typedef struct pa_cache_write_params {
   const void *key;             /* fp16 [num_tokens, num_kv_heads, head_size] */
