@@ -287,6 +287,22 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   const uint32_t hpc = args.hpc;
   const uint32_t tps = args.tokens_per_stage;
 
+  // ---- barriers first: none of this touches global memory, so in split mode it runs before
+  // the wait for the previous kernel of the stream
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < NSTAGES; ++s) {
+      mbar_init(&full_bar[s], 1);   // one arrive.expect_tx by the producer
+      mbar_init(&empty_bar[s], NW); // one arrive per consumer warp
+    }
+    for (uint32_t s = 0; s < 2; ++s) {
+      mbar_init(&sched_full[s], 1);
+      mbar_init(&sched_empty[s], NW);
+    }
+    *abort_flag = 0u;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
   // ---- the first work item of this CTA (integer bookkeeping, bit-exact); every warp keeps
   // its own cursor over the item numbering and walks it in step with its own loop
   uint32_t cta_rank = 0, num_ranks = 1;
@@ -359,20 +375,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     first.ctx = ctx;
     first.valid = true;
   }
-
-  if (threadIdx.x == 0) {
-    for (uint32_t s = 0; s < NSTAGES; ++s) {
-      mbar_init(&full_bar[s], 1);   // one arrive.expect_tx by the producer
-      mbar_init(&empty_bar[s], NW); // one arrive per consumer warp
-    }
-    for (uint32_t s = 0; s < 2; ++s) {
-      mbar_init(&sched_full[s], 1);
-      mbar_init(&sched_empty[s], NW);
-    }
-    *abort_flag = 0u;
-    mbar_fence_init();
-  }
-  __syncthreads();
 
   if (warp == 0) {
     // =========================== producer warp ===========================
@@ -524,6 +526,55 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
 #pragma unroll
       for (uint32_t j = 0; j < 4; ++j) c[j] = s_a[j] + s_b[j];
     };
+    // The same for the tiles of two stages at once, as one straight-line instruction stream:
+    // the two tiles' loads, conversions and MMA chains are independent, so they can be
+    // scheduled into each other's latencies.  Per tile the operations and their order are
+    // those of score_tile, hence the same bits.
+    auto score_tile_pair = [&](uint32_t ka_addr, uint32_t kb_addr, const uint32_t (&q)[KSTEPS][2],
+                               float (&ca)[4], float (&cb)[4]) {
+      float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+      float b0[4] = {0.f, 0.f, 0.f, 0.f}, b1[4] = {0.f, 0.f, 0.f, 0.f};
+      if constexpr (KV == KV_F16) {
+#pragma unroll
+        for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+          const uint32_t off = (ks / PAIRS_PER_SLAB) * L::SLAB_TILE;
+          uint32_t fa[4], fb[4];
+          ldmatrix_x4(fa, (ka_addr ^ ((ks % PAIRS_PER_SLAB) << 5)) + off);
+          ldmatrix_x4(fb, (kb_addr ^ ((ks % PAIRS_PER_SLAB) << 5)) + off);
+          if (ks & 1u) {
+            mma_m16n8k16(a1, fa, q[ks][0], q[ks][1]);
+            mma_m16n8k16(b1, fb, q[ks][0], q[ks][1]);
+          } else {
+            mma_m16n8k16(a0, fa, q[ks][0], q[ks][1]);
+            mma_m16n8k16(b0, fb, q[ks][0], q[ks][1]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (uint32_t qq = 0; qq < KSTEPS / 2; ++qq) {
+          uint32_t ra[4], rb[4], fa[4], fb[4];
+          ldmatrix_x4(ra, ka_addr ^ (qq << 5));
+          ldmatrix_x4(rb, kb_addr ^ (qq << 5));
+          fp8x4_to_half2x2<KV>(ra[0], fa[0], fa[2]);
+          fp8x4_to_half2x2<KV>(ra[1], fa[1], fa[3]);
+          mma_m16n8k16(a0, fa, q[2 * qq][0], q[2 * qq][1]);
+          fp8x4_to_half2x2<KV>(rb[0], fb[0], fb[2]);
+          fp8x4_to_half2x2<KV>(rb[1], fb[1], fb[3]);
+          mma_m16n8k16(b0, fb, q[2 * qq][0], q[2 * qq][1]);
+          fp8x4_to_half2x2<KV>(ra[2], fa[0], fa[2]);
+          fp8x4_to_half2x2<KV>(ra[3], fa[1], fa[3]);
+          mma_m16n8k16(a1, fa, q[2 * qq + 1][0], q[2 * qq + 1][1]);
+          fp8x4_to_half2x2<KV>(rb[2], fb[0], fb[2]);
+          fp8x4_to_half2x2<KV>(rb[3], fb[1], fb[3]);
+          mma_m16n8k16(b1, fb, q[2 * qq + 1][0], q[2 * qq + 1][1]);
+        }
+      }
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) {
+        ca[j] = a0[j] + a1[j];
+        cb[j] = b0[j] + b1[j];
+      }
+    };
     // O^T += V^T . P^T for 16 tokens: V (A operand, transposed load) from shared memory
     auto value_tile = [&](uint32_t v_base, uint32_t p_lo, uint32_t p_hi, float (&o)[KSTEPS][4]) {
       if constexpr (KV == KV_F16) {
@@ -652,7 +703,50 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const uint32_t tok_a = st * tps + my_slice * 16; // first token of this warp's tile A
         const uint32_t tok_b = tok_a + tps;
         bool released_a = false;
-        if (alive && tok_a < my_tokens) {
+        if (alive && has_b && !modifiers && tok_b + 16u <= my_tokens) {
+          // ---- the common case, two full tiles and no score modifiers, free of branches up
+          // to the rescale test; every value is computed as in the general case below
+          const uint32_t base_a = ring_base + slot_a * L::STAGE_BYTES;
+          const uint32_t base_b = ring_base + slot_b * L::STAGE_BYTES;
+          float ca[4], cb[4];
+          score_tile_pair(base_a + lm_off_a, base_b + lm_off_a, qf, ca, cb);
+          m_true[0] = fmaxf(m_true[0], quad_column_max(fmaxf(fmaxf(ca[0], ca[2]), fmaxf(cb[0], cb[2]))) * scale);
+          m_true[1] = fmaxf(m_true[1], quad_column_max(fmaxf(fmaxf(ca[1], ca[3]), fmaxf(cb[1], cb[3]))) * scale);
+          const bool stale = (m_true[0] > m_ref[0] + kRescaleThreshold) ||
+                             (m_true[1] > m_ref[1] + kRescaleThreshold);
+          if (__any_sync(0xffffffffu, stale)) {
+            const float r0 = (m_ref[0] == neg_infinity()) ? 0.f : fast_exp2(m_ref[0] - m_true[0]);
+            const float r1 = (m_ref[1] == neg_infinity()) ? 0.f : fast_exp2(m_ref[1] - m_true[1]);
+            l_run[0] *= r0;
+            l_run[1] *= r1;
+#pragma unroll
+            for (uint32_t i = 0; i < KSTEPS; ++i) {
+              acc[i][0] *= r0;
+              acc[i][1] *= r1;
+              acc[i][2] *= r0;
+              acc[i][3] *= r1;
+            }
+            m_ref[0] = m_true[0];
+            m_ref[1] = m_true[1];
+          }
+          float pa[4], pb[4];
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            pa[j] = fast_exp2(fmaf(ca[j], scale, -m_ref[j & 1u]));
+            pb[j] = fast_exp2(fmaf(cb[j], scale, -m_ref[j & 1u]));
+          }
+          l_run[0] += (pa[0] + pa[2]) + (pb[0] + pb[2]);
+          l_run[1] += (pa[1] + pa[3]) + (pb[1] + pb[3]);
+          const uint32_t pa_lo = movmatrix_trans(pack_half2(pa[0], pa[1]));
+          const uint32_t pa_hi = movmatrix_trans(pack_half2(pa[2], pa[3]));
+          const uint32_t pb_lo = movmatrix_trans(pack_half2(pb[0], pb[1]));
+          const uint32_t pb_hi = movmatrix_trans(pack_half2(pb[2], pb[3]));
+          value_tile(base_a + L::KV_TILE, pa_lo, pa_hi, acc);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty_bar[slot_a]); // stage A goes back before stage B is used
+          released_a = true;
+          value_tile(base_b + L::KV_TILE, pb_lo, pb_hi, acc);
+        } else if (alive && tok_a < my_tokens) {
           const bool act_b = has_b && tok_b < my_tokens;
           const uint32_t n_a = min(16u, my_tokens - tok_a);
           const uint32_t n_b = act_b ? min(16u, my_tokens - tok_b) : 0u;

@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from _util import make_case, run_entry
+from _util import assert_close, make_case, run_entry
 from oracle import paged_attention_oracle as oracle
 
 pytestmark = pytest.mark.gpu
@@ -160,3 +160,35 @@ def test_large_batch_takes_the_warp_merge_and_matches_the_oracle(cuda_device):
     want = oracle.paged_attention_ref(c["query"], c["key_cache"], c["value_cache"], c["block_tables"],
                                       c["context_lens"], sm_scale=c["sm_scale"])
     assert_close(run_entry("reduce", c, cuda_device)["out"], want, what="large batch")
+
+
+@pytest.mark.parametrize("d,kv", [(64, "float16"), (128, "float8_e4m3fn")])
+def test_bits_do_not_depend_on_the_position_in_a_large_batch(cuda_device, d, kv):
+    """More work than two rounds of the persistent grid: which CTA computes an item, and when, is
+    decided at run time.  A sequence must get the same bits at the front of the batch and at
+    the back, and both must match the oracle."""
+    import flash_attention_factory_b200 as pkg
+
+    psize = pkg.partition_size(d)
+    props = torch.cuda.get_device_properties(cuda_device)
+    # items = num_seqs * (kv heads / 4) * partitions: a little more than two per resident CTA
+    s, hk = 8, 8
+    parts = -(-4 * props.multi_processor_count // (s * (hk // 4))) + 1
+    ctx = [parts * psize - 7] * s
+    c = make_case(seed=61, num_seqs=s, num_heads=hk * 2, num_kv_heads=hk, head_size=d, block_size=16,
+                  context_lens=ctx, kv_dtype=kv, fp8_scale=0.5 if kv != "float16" else 1.0)
+    fwd = run_entry("reduce", c, cuda_device, poison=-3.0)
+    r = dict(c)
+    flip = torch.arange(s - 1, -1, -1)
+    r["query"] = c["query"][flip].contiguous()
+    r["block_tables"] = c["block_tables"][flip].contiguous()
+    r["context_lens"] = c["context_lens"][flip].contiguous()
+    rev = run_entry("reduce", r, cuda_device, poison=-3.0)
+    for name in ("out", "max_logits", "exp_sums", "tmp_out"):
+        assert torch.equal(fwd[name], rev[name][flip]), f"{name}: bits depend on the position in the batch"
+    for i in (0, s - 1):
+        want = oracle.paged_attention_ref(c["query"][i:i + 1], c["key_cache"], c["value_cache"],
+                                          c["block_tables"][i:i + 1], c["context_lens"][i:i + 1],
+                                          sm_scale=c["sm_scale"], fp8_scale=c["fp8_scale"])
+        assert_close(fwd["out"][i:i + 1], want, what=f"sequence {i}")
+    pkg.device_status()
