@@ -103,6 +103,8 @@ class Workload:
         cache_bytes = 2 * num_blocks * bs * hk * d * self.elt
         # rotate over several cache copies when one copy could live in L2
         self.copies = 1 if cache_bytes >= 4 * L2_BYTES else min(50, math.ceil(4 * L2_BYTES / cache_bytes))
+        if spec.get("cache_copies"):
+            self.copies = int(spec["cache_copies"])  # diagnostic: 1 copy of a small cache stays in L2
         self.fp8_scale = 1.0
         self.k, self.v = [], []
         for _ in range(self.copies):
@@ -302,6 +304,9 @@ def describe_config(a, spec: dict, variant: str, world: int, ctx) -> dict:
     blocks = sum((int(c) + bs - 1) // bs for c in ctx.tolist())
     cache_bytes = 2 * max(1, blocks) * bs * spec["kv_heads"] * spec["head_size"] * elt
     copies = 1 if cache_bytes >= 4 * L2_BYTES else min(50, math.ceil(4 * L2_BYTES / cache_bytes))
+    forced = spec.get("cache_copies")
+    if forced:
+        copies = int(forced)
     kv_bytes = int(ctx.to(torch.int64).sum()) * spec["kv_heads"] * spec["head_size"] * 2 * elt
     return {
         "workload": f"BASELINE config {a.config[1]}: {variant} variant, KV {spec['kv']}, "
@@ -312,8 +317,9 @@ def describe_config(a, spec: dict, variant: str, world: int, ctx) -> dict:
                         f"launch_kernels_{'fp8_' if fp8 else ''}loop + launch_kernels_{'fp8_' if fp8 else ''}reduce, "
                         "chosen per sequence (serving.paged_attention_auto)"),
         "kv_bytes_per_call_per_gpu": kv_bytes, "cache_copies_rotated": copies,
-        "l2_policy": "inputs larger than L2" if copies == 1 else
-                     f"rotating over {copies} cache copies (> 4x L2 in total)",
+        "l2_policy": (f"DIAGNOSTIC: {copies} cache copies forced, inputs may stay in L2" if forced else
+                      "inputs larger than L2" if copies == 1 else
+                      f"rotating over {copies} cache copies (> 4x L2 in total)"),
         "block_order": spec.get("block_order", "random"),
         "launch": "cuda graph replay" if getattr(a, "cuda_graph", False) else "direct",
         "sharding": "none" if world == 1 else
@@ -349,6 +355,9 @@ def main() -> None:
     ap.add_argument("--e2e-mode", default="step", choices=["torch", "step", "direct"],
                     help="end-to-end leg: torch copies + enqueue, one pa_decode_step_host call per step, "
                          "or the same with the kernels writing the result into pinned host memory")
+    ap.add_argument("--cache-copies", type=int, default=None,
+                    help="diagnostic: number of KV-cache copies the steps rotate over (1 with a small cache "
+                         "measures the kernel fed from L2, not an HBM figure)")
     ap.add_argument("--block-order", default=None, choices=["random", "sequential"],
                     help="physical placement of a sequence's blocks (default: a random permutation)")
     ap.add_argument("--num-seqs", type=int, default=None,
@@ -374,7 +383,9 @@ def main() -> None:
             spec[key] = val
     if a.block_order is not None:
         spec["block_order"] = a.block_order
-    overridden = any(v is not None for v in (a.num_seqs, a.kv, a.head_size, a.heads, a.kv_heads, a.block_size, a.block_order))
+    if a.cache_copies is not None:
+        spec["cache_copies"] = a.cache_copies
+    overridden = any(v is not None for v in (a.num_seqs, a.kv, a.head_size, a.heads, a.kv_heads, a.block_size, a.block_order, a.cache_copies))
     variant = a.variant or pick_variant(spec)
 
     if a.impl == "reference":
