@@ -156,9 +156,9 @@ inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_cou
   return cs;
 }
 
-template <int D, int KV>
+template <int D, int KV, int NWARPS = 4>
 AttnArgs make_attn_args(const pa_params *p, bool loop_mode = false, int sm_count = 0) {
-  using policy = paged_attention_policy_v2<D, KV>;
+  using policy = paged_attention_policy_v2<D, KV, NWARPS>;
   AttnArgs a{};
   a.query = static_cast<const __half *>(p->query);
   a.out = static_cast<__half *>(p->out);
@@ -177,7 +177,9 @@ AttnArgs make_attn_args(const pa_params *p, bool loop_mode = false, int sm_count
   a.block_shift = log2_pow2(p->block_size);
   // KV heads per CTA: with 4 a warp owns a head and nothing is merged across warps
   a.hpc = (p->num_kv_heads % 4 == 0) ? 4u : ((p->num_kv_heads % 2 == 0) ? 2u : 1u);
-  {
+  if (NWARPS == 8) {
+    a.hpc = 8u; // the wide CTA is only chosen for num_kv_heads % 8 == 0: a warp per head
+  } else {
     // debugging knob: PA_FORCE_HPC=1|2 lowers the number of KV heads per CTA
     static const int forced = [] {
       const char *e = std::getenv("PA_FORCE_HPC");
@@ -212,15 +214,16 @@ AttnArgs make_attn_args(const pa_params *p, bool loop_mode = false, int sm_count
 }
 
 // Enqueues the attention kernel of one (D, KV, MODE) instantiation.
-template <int D, int KV, int MODE>
+template <int D, int KV, int MODE, int NWARPS = 4>
 int enqueue_attention(const pa_params *p, cudaStream_t stream) {
-  using L = SmemLayout<D, KV>;
+  static_assert(NWARPS == 4 || MODE == MODE_SPLIT, "the wide CTA exists for the split variant only");
+  using L = SmemLayout<D, KV, NWARPS>;
   using policy = typename L::policy;
   DeviceInfo dev{};
   if (int rc = get_device_info(&dev)) return rc;
   if (dev.cc_major < 10) return fail(PA_ERR_CUDA, "this library needs an sm_100a device");
 
-  AttnArgs args = make_attn_args<D, KV>(p, MODE == MODE_LOOP, dev.sm_count);
+  AttnArgs args = make_attn_args<D, KV, NWARPS>(p, MODE == MODE_LOOP, dev.sm_count);
   if (MODE == MODE_SPLIT) {
     static std::atomic<uint32_t> next_slot{0}; // per kernel instantiation, like its counters
     args.sched_slot = next_slot.fetch_add(1, std::memory_order_relaxed) % kSchedSlots;
@@ -229,7 +232,7 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
   if (int rc = encode_cache_map<D, KV>(&map_k, p->key_cache, p, args.rows_per_box, args.heads_per_box)) return rc;
   if (int rc = encode_cache_map<D, KV>(&map_v, p->value_cache, p, args.rows_per_box, args.heads_per_box)) return rc;
 
-  auto kernel = paged_attention_kernel<D, KV, MODE>;
+  auto kernel = paged_attention_kernel<D, KV, MODE, NWARPS>;
   static thread_local int configured_device = -1;
   int device = 0;
   PA_CUDA_TRY(cudaGetDevice(&device));
@@ -349,9 +352,35 @@ int run_timed(cudaStream_t stream, float *us_out, F1 first, F2 second, bool has_
   return PA_OK;
 }
 
+// Wide CTA (8 MMA warps, 8 KV heads per work item, one CTA per SM) or the default?  Wide for
+// FP8 caches in the split variant when the KV heads come in eights and the launch has work
+// for at least two rounds of one CTA per SM; everything else, small launches included, runs
+// the default shape, whose work items are half as large.  Both shapes give the same bits.
+template <int KV, int MODE>
+bool wants_wide_cta(const pa_params *p) {
+  if (KV == KV_F16 || MODE != MODE_SPLIT || p->num_kv_heads % 8u != 0u) return false;
+  // debugging knob: PA_WIDE_CTA=0 never, 1 whenever the head count allows
+  static const int knob = [] {
+    const char *e = std::getenv("PA_WIDE_CTA");
+    return e ? std::atoi(e) : -1;
+  }();
+  if (knob == 0) return false;
+  if (knob == 1) return true;
+  DeviceInfo dev{};
+  if (get_device_info(&dev) != PA_OK) return false;
+  const uint64_t items = static_cast<uint64_t>(p->num_kv_heads / 8u) * p->max_num_partitions * p->num_seqs;
+  return items >= 2ull * static_cast<uint64_t>(dev.sm_count);
+}
+
 // head-size dispatch for one KV type and mode
 template <int KV, int MODE>
 int dispatch_head_size(const pa_params *p, cudaStream_t stream) {
+  if constexpr (KV != KV_F16 && MODE == MODE_SPLIT) {
+    if (wants_wide_cta<KV, MODE>(p)) {
+      if (p->head_size == 128) return enqueue_attention<128, KV, MODE, 8>(p, stream);
+      return enqueue_attention<64, KV, MODE, 8>(p, stream);
+    }
+  }
   if (p->head_size == 128) return enqueue_attention<128, KV, MODE>(p, stream);
   return enqueue_attention<64, KV, MODE>(p, stream);
 }

@@ -70,7 +70,7 @@ struct AttnArgs {
   uint32_t max_blocks_per_seq;
   uint32_t max_num_partitions;
   uint32_t block_shift;      // log2(block_size)
-  uint32_t hpc;              // KV heads per CTA: 1, 2 or 4 (divides num_kv_heads)
+  uint32_t hpc;              // KV heads per CTA: 1, 2, 4, or 8 in the wide CTA (divides num_kv_heads)
   uint32_t tokens_per_stage; // 64 / hpc
   uint32_t rows_per_box;     // min(block_size, tokens_per_stage)
   uint32_t boxes_per_stage;  // hpc * tokens_per_stage / rows_per_box: 1, 2 or 4
@@ -102,9 +102,9 @@ constexpr float kLog2e = 1.4426950408889634f;
 // the rescaling of the accumulator.
 constexpr float kRescaleThreshold = 8.0f;
 
-template <int D, int KV>
+template <int D, int KV, int NWARPS = 4>
 struct SmemLayout {
-  using policy = paged_attention_policy_v2<D, KV>;
+  using policy = paged_attention_policy_v2<D, KV, NWARPS>;
   using geo = typename policy::geometry;
   static constexpr uint32_t NW = policy::consumer_warps;
   static constexpr uint32_t ROWS = policy::tokens_per_stage; // 64 rows: hpc heads x 64/hpc tokens
@@ -113,7 +113,7 @@ struct SmemLayout {
   static constexpr uint32_t KV_TILE = geo::num_slabs * SLAB_TILE; // K (or V) of one stage
   static constexpr uint32_t STAGE_BYTES = 2 * KV_TILE;
   static constexpr uint32_t RING_BYTES = NSTAGES * STAGE_BYTES;
-  static_assert(NW == 4, "warp <-> (head, token slice) mapping is written for four consumer warps");
+  static_assert(NW == 4 || NW == 8, "warp <-> (head, token slice) mapping: 4 warps, or 8 with one head per warp");
   // split mode, fewer than 4 heads per CTA: two O[8][D] buffers filled in a fixed order
   static constexpr uint32_t MERGE_OFFSET = RING_BYTES;
   static constexpr uint32_t MERGE_BYTES = 2 * 8 * D * 4;
@@ -253,12 +253,12 @@ __device__ __forceinline__ void load_q_fragments(uint32_t (&qf)[D / 16][2], cons
   }
 }
 
-template <int D, int KV, int MODE>
-__global__ void __launch_bounds__(paged_attention_policy_v2<D, KV>::threads_per_cta,
-                                  paged_attention_policy_v2<D, KV>::ctas_per_sm)
+template <int D, int KV, int MODE, int NWARPS = 4>
+__global__ void __launch_bounds__(paged_attention_policy_v2<D, KV, NWARPS>::threads_per_cta,
+                                  paged_attention_policy_v2<D, KV, NWARPS>::ctas_per_sm)
 paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const AttnArgs args) {
-  using L = SmemLayout<D, KV>;
+  using L = SmemLayout<D, KV, NWARPS>;
   using policy = typename L::policy;
   using geo = typename L::geo;
   constexpr uint32_t NW = L::NW;

@@ -37,7 +37,12 @@ struct kv_tile_geometry {
 
 // One policy serves the loop and the reduce variants; query_group_size is a
 // run-time value (1..8) because the group occupies the N=8 extent of the MMA.
-template <uint32_t max_head_size_, int kv_type_>
+//
+// consumer_warps_ selects the CTA shape: 4 MMA warps and two CTAs per SM (default), or 8 MMA
+// warps and one CTA per SM with a ring twice as large.  The wide shape lets a CTA take eight KV
+// heads at once, which doubles the size of every TMA box; a warp does the same work on its
+// head in both shapes, so the results are the same bit for bit.
+template <uint32_t max_head_size_, int kv_type_, uint32_t consumer_warps_ = 4>
 struct paged_attention_policy_v2 : paged_attention_base_policy {
   using geometry = kv_tile_geometry<max_head_size_, kv_type_>;
   static constexpr uint32_t max_head_size = max_head_size_;
@@ -49,7 +54,8 @@ struct paged_attention_policy_v2 : paged_attention_base_policy {
   static constexpr uint32_t max_partitions_per_sg = max_head_size_ == 64 ? 16u : 4u;
 
   // ---- sm_100a geometry ----
-  static constexpr uint32_t consumer_warps = 4;                     // MMA warps
+  static_assert(consumer_warps_ == 4 || consumer_warps_ == 8, "4 or 8 MMA warps");
+  static constexpr uint32_t consumer_warps = consumer_warps_;       // MMA warps
   static constexpr uint32_t tokens_per_warp = 16;                   // M extent of m16n8k16
   static constexpr uint32_t tokens_per_stage = consumer_warps * tokens_per_warp; // 64
   static constexpr uint32_t threads_per_cta = (consumer_warps + 1) * 32; // + 1 TMA warp
@@ -58,8 +64,11 @@ struct paged_attention_policy_v2 : paged_attention_base_policy {
   // 6 stages of 16 KB for FP8).  Measured on B200: three CTAs with 64 KB rings were no faster
   // for FP8 (the kernel is bound by HBM and by the depth of the ring, not by issue slots) and
   // left the loop variant with too shallow a ring per CTA.
-  static constexpr uint32_t ctas_per_sm = 2u;
-  static constexpr uint32_t ring_budget = 96u * 1024u;
+  // Eight MMA warps: one CTA per SM with the whole 192 KB; measured 1-2 % faster than two
+  // narrow CTAs on FP8 caches with 8 KV heads (16 KB boxes instead of 8 KB), and 5 % slower
+  // when its ring is cut to 128 KB.
+  static constexpr uint32_t ctas_per_sm = consumer_warps_ == 8 ? 1u : 2u;
+  static constexpr uint32_t ring_budget = (consumer_warps_ == 8 ? 192u : 96u) * 1024u;
   static constexpr uint32_t ring_stages_raw = ring_budget / stage_bytes;
   static constexpr uint32_t ring_stages = ring_stages_raw > 8u ? 8u : ring_stages_raw;
   static_assert(ring_stages >= 2, "ring too shallow");

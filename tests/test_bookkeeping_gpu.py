@@ -186,6 +186,14 @@ def test_bits_do_not_depend_on_the_position_in_a_large_batch(cuda_device, d, kv)
     rev = run_entry("reduce", r, cuda_device, poison=-3.0)
     for name in ("out", "max_logits", "exp_sums", "tmp_out"):
         assert torch.equal(fwd[name], rev[name][flip]), f"{name}: bits depend on the position in the batch"
+    # alone, the sequence is a small launch (FP8: the default CTA shape instead of the wide one)
+    solo = dict(c)
+    solo["query"] = c["query"][3:4].contiguous()
+    solo["block_tables"] = c["block_tables"][3:4].contiguous()
+    solo["context_lens"] = c["context_lens"][3:4].contiguous()
+    alone = run_entry("reduce", solo, cuda_device, poison=-3.0)
+    for name in ("out", "max_logits", "exp_sums", "tmp_out"):
+        assert torch.equal(fwd[name][3:4], alone[name]), f"{name}: bits depend on the rest of the batch"
     for i in (0, s - 1):
         want = oracle.paged_attention_ref(c["query"][i:i + 1], c["key_cache"], c["value_cache"],
                                           c["block_tables"][i:i + 1], c["context_lens"][i:i + 1],
