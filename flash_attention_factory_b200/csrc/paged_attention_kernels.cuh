@@ -116,7 +116,7 @@ struct SmemLayout {
   static_assert(NW == 4 || NW == 8, "warp <-> (head, token slice) mapping: 4 warps, or 8 with one head per warp");
   // split mode, fewer than 4 heads per CTA: two O[8][D] buffers filled in a fixed order
   static constexpr uint32_t MERGE_OFFSET = RING_BYTES;
-  static constexpr uint32_t MERGE_BYTES = 2 * 8 * D * 4;
+  static constexpr uint32_t MERGE_BYTES = (NWARPS == 8) ? 0 : 2 * 8 * D * 4; // the wide CTA never merges
   // per-warp (reference max, true max, sum) of the 8 query columns, double-buffered by item parity
   static constexpr uint32_t WARP_STATS_OFFSET = MERGE_OFFSET + MERGE_BYTES;
   static constexpr uint32_t WARP_STATS_FLOATS = 3 * NW * 8;

@@ -65,8 +65,9 @@ struct paged_attention_policy_v2 : paged_attention_base_policy {
   // for FP8 (the kernel is bound by HBM and by the depth of the ring, not by issue slots) and
   // left the loop variant with too shallow a ring per CTA.
   // Eight MMA warps: one CTA per SM with the whole 192 KB; measured 1-2 % faster than two
-  // narrow CTAs on FP8 caches with 8 KV heads (16 KB boxes instead of 8 KB), and 5 % slower
-  // when its ring is cut to 128 KB.
+  // narrow CTAs on FP8 caches with 8 KV heads (16 KB boxes instead of 8 KB), 5 % slower
+  // when its ring is cut to 128 KB and no faster with 224 KB; on fp16 caches (3 stages of 64 KB) it was
+  // 2 % slower than the default shape and is not used there.
   static constexpr uint32_t ctas_per_sm = consumer_warps_ == 8 ? 1u : 2u;
   static constexpr uint32_t ring_budget = (consumer_warps_ == 8 ? 192u : 96u) * 1024u;
   static constexpr uint32_t ring_stages_raw = ring_budget / stage_bytes;
