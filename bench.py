@@ -564,10 +564,10 @@ def main() -> None:
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch, from the ncu
 # captures summarised under profiles/ (None until a capture exists for the workload)
 TRAFFIC_BYTES: dict = {
-    # profiles/paged_attention_kernel_split_fp16_c2_small.md: 16 x (268.54 + 3.81) MB
-    ("c2", "reduce"): 4_357_600_000,
-    # profiles/paged_attention_kernel_split_e4m3_c4_small.md: 8 x (134.33 + 3.71) MB
-    ("c4", "reduce"): 1_104_300_000,
+    # profiles/paged_attention_kernel_split_fp16_c2_small.md: 4 x (1073.96 + 3.82) MB
+    ("c2", "reduce"): 4_311_100_000,
+    # profiles/paged_attention_kernel_split_e4m3_c4_small.md: 2 x (537.13 + 5.65) MB
+    ("c4", "reduce"): 1_085_600_000,
 }
 
 
