@@ -178,10 +178,13 @@ class Workload:
         return 2 if self.variant == "reduce" else 1
 
 
-def shard_by_kv_length(ctx: torch.Tensor, world: int, rank: int) -> torch.Tensor:
-    """Contiguous range of sequences whose cumulative KV length falls in this rank's share."""
-    from flash_attention_factory_b200.sharding import shard_sequences_by_kv_length
+def shard_by_kv_length(ctx: torch.Tensor, world: int, rank: int, scheme: str = "contiguous") -> torch.Tensor:
+    """This rank's sequences: the contiguous range whose cumulative KV length falls in its share,
+    or (scheme "lpt") the ids dealt longest-first to the lightest rank."""
+    from flash_attention_factory_b200.sharding import shard_sequences_by_kv_length, shard_sequences_lpt
 
+    if scheme == "lpt":
+        return ctx[torch.tensor(shard_sequences_lpt(ctx.tolist(), world)[rank], dtype=torch.long)].clone()
     lo, hi = shard_sequences_by_kv_length(ctx.tolist(), world)[rank]
     return ctx[lo:hi].clone()
 
@@ -323,7 +326,8 @@ def describe_config(a, spec: dict, variant: str, world: int, ctx) -> dict:
         "block_order": spec.get("block_order", "random"),
         "launch": "cuda graph replay" if getattr(a, "cuda_graph", False) else "direct",
         "sharding": "none" if world == 1 else
-                    ("sequences split by cumulative KV length" if strong else "one shard per GPU"),
+                    (("sequences dealt longest-first to the lightest GPU" if getattr(a, "shard", "") == "lpt"
+                      else "sequences split by cumulative KV length") if strong else "one shard per GPU"),
     }
 
 
@@ -355,6 +359,9 @@ def main() -> None:
     ap.add_argument("--e2e-mode", default="step", choices=["torch", "step", "direct"],
                     help="end-to-end leg: torch copies + enqueue, one pa_decode_step_host call per step, "
                          "or the same with the kernels writing the result into pinned host memory")
+    ap.add_argument("--shard", default="contiguous", choices=["contiguous", "lpt"],
+                    help="config c5 on several GPUs: contiguous ranges balanced on cumulative KV length "
+                         "(default) or longest-first assignment to the lightest GPU")
     ap.add_argument("--cache-copies", type=int, default=None,
                     help="diagnostic: number of KV-cache copies the steps rotate over (1 with a small cache "
                          "measures the kernel fed from L2, not an HBM figure)")
@@ -407,7 +414,7 @@ def main() -> None:
 
     ctx_all = draw_context_lens(spec, seed=int(a.config[1]))
     strong = a.config == "c5"
-    ctx = shard_by_kv_length(ctx_all, world, rank) if (strong and world > 1) else ctx_all
+    ctx = shard_by_kv_length(ctx_all, world, rank, a.shard) if (strong and world > 1) else ctx_all
     w = Workload(spec, ctx, device, seed=1000 * int(a.config[1]) + rank, variant=variant)
 
     def sync_all():

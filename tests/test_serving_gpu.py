@@ -22,7 +22,7 @@ def test_auto_matches_oracle_and_single_variant_bits(cuda_device, kv):
     bt, cl = c["block_tables"].to(dev), c["context_lens"].to(dev)
     sinks = c["sinks"].to(dev)
     out = torch.full_like(q, float("nan"))
-    plan = AutoDecodePlan(ctx, 16, 128, 16, bt.size(1), dev)
+    plan = AutoDecodePlan(ctx, 16, 128, 16, bt.size(1), dev, fold_short_fraction=0.0)  # strictly per sequence
     assert plan.loop is not None and plan.reduce is not None
     for _ in range(2):  # the plan is reusable
         paged_attention_auto(plan, out, q, k, v, bt, cl, 4, c["sm_scale"], c["fp8_scale"], sinks)
@@ -35,6 +35,16 @@ def test_auto_matches_oracle_and_single_variant_bits(cuda_device, kv):
     by_variant = {vname: run_entry(vname, c, dev)["out"] for vname in ("loop", "reduce")}
     for i, n in enumerate(ctx):
         assert torch.equal(out[i].cpu(), by_variant[choose_variant(n)][i]), f"sequence {i}"
+    # default plan: the three short sequences hold 5 % of the tokens and are folded into the split launch
+    folded = AutoDecodePlan(ctx, 16, 128, 16, bt.size(1), dev)
+    assert folded.loop is None and folded.reduce.count == len(ctx)
+    out2 = torch.full_like(q, float("nan"))
+    paged_attention_auto(folded, out2, q, k, v, bt, cl, 4, c["sm_scale"], c["fp8_scale"], sinks)
+    torch.cuda.synchronize(dev)
+    assert torch.equal(out2.cpu(), by_variant["reduce"])
+    # a batch of short sequences only is one loop launch
+    short = AutoDecodePlan([30, 500, 1, 400], 16, 128, 16, bt.size(1), dev)
+    assert short.reduce is None and short.loop.count == 4
 
 
 def test_decode_step_io_round_trip(cuda_device):

@@ -81,3 +81,21 @@ def test_two_rank_gloo_shards_partition_the_batch():
         assert p.exitcode == 0
     assert sum(p[0] for p in parts) == total and sum(p[1] for p in parts) == n
     assert abs(parts[0][0] - parts[1][0]) <= 2 * 4096
+
+
+def test_lpt_sharding_is_a_balanced_partition():
+    import random
+
+    from flash_attention_factory_b200.sharding import shard_sequences_lpt
+
+    rng = random.Random(7)
+    lens = [max(16, min(32768, int(rng.lognormvariate(7.5, 1.0)))) for _ in range(1024)]
+    for world in (1, 2, 4, 8):
+        shards = shard_sequences_lpt(lens, world)
+        assert sorted(i for s in shards for i in s) == list(range(len(lens)))  # a partition
+        assert all(s == sorted(s) for s in shards)
+        loads = [sum(lens[i] for i in s) for s in shards]
+        assert max(loads) - min(loads) <= max(lens)
+        assert max(loads) <= 1.001 * sum(lens) / world
+    assert shard_sequences_lpt([], 3) == [[], [], []]
+    assert shard_sequences_lpt([5, 5, 5], 2) == [[0, 2], [1]]  # ties: lower id first, lower rank first
