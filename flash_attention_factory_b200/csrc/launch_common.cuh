@@ -242,7 +242,7 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
   }
 
   cudaLaunchConfig_t cfg{};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   cfg.blockDim = dim3(policy::threads_per_cta, 1, 1);
   cfg.dynamicSmemBytes = L::DYN_SMEM;
   cfg.stream = stream;
@@ -270,8 +270,10 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
     attr[0].val.clusterDim.x = cs;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
   }
   PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_k, map_v, args));
   return PA_OK;

@@ -323,6 +323,12 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     cg::cluster_group cluster = cg::this_cluster();
     cta_rank = cluster.block_rank();
     num_ranks = cluster.num_blocks();
+    // programmatic dependent launch, as in split mode: the next kernel of the stream may be
+    // scheduled while this one runs, and this one touches no global memory before the
+    // previous kernel of the stream has completed (back-to-back calls on tiny batches are
+    // bound by launch latency otherwise)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // Clusters start in block-index order.  With ragged lengths a long sequence that starts
     // last leaves the machine idle behind it, so block index z is mapped to the z-th sequence
     // in (approximately) descending length: 16 length classes, longest class first, position
