@@ -48,12 +48,22 @@ __device__ __forceinline__ void store_converted(void *dst_row, uint32_t elem, ui
 }
 
 // One CTA per new token; a thread moves 8 elements of K and 8 of V per step.
-template <int KV>
+template <int KV, bool CHAINED>
 __global__ void __launch_bounds__(128)
 reshape_and_cache_kernel(const __half *__restrict__ key, const __half *__restrict__ value,
                          void *__restrict__ key_cache, void *__restrict__ value_cache,
                          const int64_t *__restrict__ slot_mapping, uint32_t row_elems, uint64_t num_slots,
                          float scale, float exact_rcp) {
+  // CHAINED (decode-sized appends): programmatic dependent launch.  The attention kernel that
+  // follows in a decode step may be scheduled while this grid runs (it waits for this grid's
+  // completion before its first read), and this grid reads nothing before its own predecessor
+  // in the stream has completed.  Prefill-sized appends, tens of thousands of CTAs of about a
+  // microsecond each, run the plain form: the two instructions per CTA measured 6 % slower on
+  // the FP8 caches there.
+  if constexpr (CHAINED) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
   const uint32_t token = blockIdx.x;
   const int64_t slot = slot_mapping[token];
   if (slot < 0 || static_cast<uint64_t>(slot) >= num_slots) return; // padding token / out of range
@@ -97,16 +107,28 @@ extern "C" PA_API int pa_reshape_and_cache(const pa_cache_write_params *p, void 
       exact_rcp = 1.f / p->fp8_scale;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const dim3 grid(p->num_tokens), block(128);
   const uint32_t re = static_cast<uint32_t>(row_elems);
   const __half *k = static_cast<const __half *>(p->key);
   const __half *v = static_cast<const __half *>(p->value);
-  if (p->kv_dtype == PA_KV_F16)
-    reshape_and_cache_kernel<KV_F16><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, 1.f, 1.f);
-  else if (p->kv_dtype == PA_KV_FP8_E5M2)
-    reshape_and_cache_kernel<KV_E5M2><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, p->fp8_scale, exact_rcp);
-  else
-    reshape_and_cache_kernel<KV_E4M3><<<grid, block, 0, s>>>(k, v, p->key_cache, p->value_cache, p->slot_mapping, re, num_slots, p->fp8_scale, exact_rcp);
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  cfg.gridDim = dim3(p->num_tokens, 1, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.stream = s;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  const bool chained = p->num_tokens <= 4096u;
+  cfg.numAttrs = chained ? 1 : 0;
+  const float scale = (p->kv_dtype == PA_KV_F16) ? 1.f : p->fp8_scale;
+  const float rcp = (p->kv_dtype == PA_KV_F16) ? 1.f : exact_rcp;
+  auto kernel = (p->kv_dtype == PA_KV_F16)
+                    ? (chained ? reshape_and_cache_kernel<KV_F16, true> : reshape_and_cache_kernel<KV_F16, false>)
+                : (p->kv_dtype == PA_KV_FP8_E5M2)
+                    ? (chained ? reshape_and_cache_kernel<KV_E5M2, true> : reshape_and_cache_kernel<KV_E5M2, false>)
+                    : (chained ? reshape_and_cache_kernel<KV_E4M3, true> : reshape_and_cache_kernel<KV_E4M3, false>);
+  PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, k, v, p->key_cache, p->value_cache, p->slot_mapping, re,
+                                 num_slots, scale, rcp));
   PA_CUDA_TRY(cudaGetLastError());
   return PA_OK;
 }

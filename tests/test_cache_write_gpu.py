@@ -74,3 +74,24 @@ def test_decode_step_append_then_attend(cuda_device, kv):
                                       sm_scale=c["sm_scale"], fp8_scale=c["fp8_scale"])
     for variant in ("loop", "reduce"):
         assert_close(run_entry(variant, c2, cuda_device)["out"], want, what=f"append+attend/{kv}/{variant}")
+
+
+@pytest.mark.parametrize("kv,scale", [("float16", 1.0), ("float8_e4m3fn", 0.5), ("float8_e5m2", 0.3)])
+def test_prefill_sized_append_is_bit_exact(cuda_device, kv, scale):
+    """More than 4096 tokens take the plain (not launch-chained) form of the kernel."""
+    from flash_attention_factory_b200.cache_ops import reshape_and_cache
+
+    g = torch.Generator().manual_seed(77)
+    hk, d, bs, nb, t = 4, 128, 16, 400, 5000
+    dt = torch.float16 if kv == "float16" else FP8_DTYPES[kv]
+    key = (torch.randn(t, hk, d, generator=g) * scale * 20).to(torch.float16)
+    value = (torch.randn(t, hk, d, generator=g) * scale * 20).to(torch.float16)
+    kc = torch.zeros(nb, bs, hk, d, dtype=torch.float16).to(dt)
+    vc = torch.zeros(nb, bs, hk, d, dtype=torch.float16).to(dt)
+    slots = torch.randperm(nb * bs, generator=g)[:t].to(torch.int64)
+    want_k, want_v = oracle.reshape_and_cache_ref(key, value, kc, vc, slots, scale)
+    dk, dv = kc.to(cuda_device), vc.to(cuda_device)
+    reshape_and_cache(key.to(cuda_device), value.to(cuda_device), dk, dv, slots.to(cuda_device), scale)
+    torch.cuda.synchronize(cuda_device)
+    assert torch.equal(_bits(dk.cpu()), _bits(want_k))
+    assert torch.equal(_bits(dv.cpu()), _bits(want_v))
