@@ -367,7 +367,7 @@ def main() -> None:
     ap.add_argument("--heads", type=int, default=None, help="override the number of query heads")
     ap.add_argument("--kv-heads", type=int, default=None, help="override the number of KV heads")
     ap.add_argument("--block-size", type=int, default=None, choices=[16, 32, 64, 128])
-    ap.add_argument("--e2e-mode", default="step", choices=["torch", "step", "direct"],
+    ap.add_argument("--e2e-mode", default="direct", choices=["torch", "step", "direct"],
                     help="end-to-end leg: torch copies + enqueue, one pa_decode_step_host call per step, "
                          "or the same with the kernels writing the result into pinned host memory")
     ap.add_argument("--shard", default="contiguous", choices=["contiguous", "lpt"],
