@@ -6,6 +6,7 @@
 // paged_attention_reduce/launch_kernels_reduce.h:18-78,80-197).
 #pragma once
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -370,7 +371,13 @@ bool wants_wide_cta(const pa_params *p) {
   if (knob == 1) return true;
   DeviceInfo dev{};
   if (get_device_info(&dev) != PA_OK) return false;
-  const uint64_t items = static_cast<uint64_t>(p->num_kv_heads / 8u) * p->max_num_partitions * p->num_seqs;
+  // partitions per sequence: the scratch extent, cut down by the context-length hint if given
+  uint32_t parts = p->max_num_partitions;
+  if (p->max_context_len != 0u) {
+    const uint32_t psize = (p->head_size == 64u) ? 256u : 512u;
+    parts = std::min(parts, divide_round_up(p->max_context_len, psize));
+  }
+  const uint64_t items = static_cast<uint64_t>(p->num_kv_heads / 8u) * parts * p->num_seqs;
   return items >= 2ull * static_cast<uint64_t>(dev.sm_count);
 }
 
