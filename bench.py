@@ -311,7 +311,8 @@ def measured_hbm_peak() -> tuple[float, str]:
 
 def describe_config(a, spec: dict, variant: str, world: int, ctx) -> dict:
     """The `config` object of the JSON line; identical for the two --impl arms."""
-    strong = a.config == "c5"
+    by_heads = getattr(a, "shard", "") == "heads" and world > 1
+    strong = a.config == "c5" or by_heads
     fp8 = spec["kv"] != "float16"
     elt = 1 if fp8 else 2
     bs = spec["block_size"]
@@ -337,7 +338,8 @@ def describe_config(a, spec: dict, variant: str, world: int, ctx) -> dict:
         "block_order": spec.get("block_order", "random"),
         "launch": "cuda graph replay" if getattr(a, "cuda_graph", False) else "direct",
         "sharding": "none" if world == 1 else
-                    (("sequences dealt longest-first to the lightest GPU" if getattr(a, "shard", "") == "lpt"
+                    ("KV heads split evenly over the GPUs (heads shown are per GPU)" if by_heads else
+                     ("sequences dealt longest-first to the lightest GPU" if getattr(a, "shard", "") == "lpt"
                       else "sequences split by cumulative KV length") if strong else "one shard per GPU"),
     }
 
@@ -370,9 +372,11 @@ def main() -> None:
     ap.add_argument("--e2e-mode", default="direct", choices=["torch", "step", "direct"],
                     help="end-to-end leg: torch copies + enqueue, one pa_decode_step_host call per step, "
                          "or the same with the kernels writing the result into pinned host memory")
-    ap.add_argument("--shard", default="contiguous", choices=["contiguous", "lpt"],
-                    help="config c5 on several GPUs: contiguous ranges balanced on cumulative KV length "
-                         "(default) or longest-first assignment to the lightest GPU")
+    ap.add_argument("--shard", default="contiguous", choices=["contiguous", "lpt", "heads"],
+                    help="several GPUs: config c5 is split by sequence, in contiguous ranges balanced on "
+                         "cumulative KV length (default) or longest-first to the lightest GPU (lpt); "
+                         "'heads' splits any config by KV head instead (few very long sequences): every "
+                         "GPU holds num_kv_heads / N heads of all sequences")
     ap.add_argument("--cache-copies", type=int, default=None,
                     help="diagnostic: number of KV-cache copies the steps rotate over (1 with a small cache "
                          "measures the kernel fed from L2, not an HBM figure)")
@@ -424,8 +428,17 @@ def main() -> None:
         dist.init_process_group(backend="nccl", device_id=device)
 
     ctx_all = draw_context_lens(spec, seed=int(a.config[1]))
-    strong = a.config == "c5"
-    ctx = shard_by_kv_length(ctx_all, world, rank, a.shard) if (strong and world > 1) else ctx_all
+    by_heads = a.shard == "heads" and world > 1
+    if by_heads:
+        from flash_attention_factory_b200.sharding import shard_kv_heads
+
+        lo, hi = shard_kv_heads(spec["kv_heads"], world)[rank]
+        if (hi - lo) * world != spec["kv_heads"]:
+            raise SystemExit("--shard heads needs num_kv_heads divisible by the number of GPUs")
+        group = spec["heads"] // spec["kv_heads"]
+        spec["kv_heads"], spec["heads"] = hi - lo, (hi - lo) * group  # this rank's slice of both caches
+    strong = a.config == "c5" or by_heads
+    ctx = shard_by_kv_length(ctx_all, world, rank, a.shard) if (a.config == "c5" and world > 1 and not by_heads) else ctx_all
     w = Workload(spec, ctx, device, seed=1000 * int(a.config[1]) + rank, variant=variant)
 
     def sync_all():
