@@ -21,7 +21,9 @@
 // neighbouring KV heads at once: with hpc = 4 a warp owns one KV head and sees
 // every token of the item, so nothing has to be merged across warps; with
 // fewer heads the warps split the tokens and merge through shared memory in a
-// fixed order.  The GQA query group sits on the N=8 extent of mma.m16n8k16 and
+// fixed order.  A second shape of the same kernel (NWARPS = 8: warps 1..8, hpc = 8,
+// one CTA per SM, a ring twice as large) serves FP8 caches in split mode; a warp
+// does the same work on its head in both shapes, so they give the same bits.  The GQA query group sits on the N=8 extent of mma.m16n8k16 and
 // the tokens on M, so a KV byte is read from HBM once for the whole group:
 //   S^T[tok, g] = K[tok, d] . Q^T[d, g]          (A = K via ldmatrix)
 //   O^T[d, g]  += V^T[d, tok] . P^T[tok, g]      (A = V via ldmatrix.trans)
