@@ -534,7 +534,7 @@ def main() -> None:
     # ---- read rate of a kernel that only reads, same pools, one launch, this GPU, this run
     read_gbs, bulk_gbs, read_bytes = None, None, 0
     if rank == 0:
-        from flash_attention_factory_b200 import _cabi
+        from flash_attention_factory_b200 import _test_aids as _cabi
 
         kp, vp = w.k[0], w.v[0]
         read_bytes = (kp.numel() + vp.numel()) * kp.element_size()

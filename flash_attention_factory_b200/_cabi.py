@@ -35,8 +35,6 @@ EXPORTED_SYMBOLS = (
     "pa_partition_size",
     "pa_last_error",
     "pa_device_status",
-    "pa_selftest_wait_timeout",
-    "pa_measure_read_bandwidth",
     "pa_decode_step_host",
     "pa_version",
 )
@@ -167,12 +165,6 @@ def load_library() -> ctypes.CDLL:
     lib.pa_last_error.restype = ctypes.c_char_p
     lib.pa_device_status.argtypes = []
     lib.pa_device_status.restype = ctypes.c_int
-    lib.pa_selftest_wait_timeout.argtypes = [ctypes.c_uint32]
-    lib.pa_selftest_wait_timeout.restype = ctypes.c_int
-    lib.pa_measure_read_bandwidth.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_uint64,
-                                              ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
-                                              ctypes.POINTER(ctypes.c_float)]
-    lib.pa_measure_read_bandwidth.restype = ctypes.c_int
     lib.pa_decode_step_host.argtypes = [ctypes.c_int32, ctypes.POINTER(PaParams), ctypes.POINTER(PaHostStep),
                                         ctypes.c_void_p, ctypes.c_int32]
     lib.pa_decode_step_host.restype = ctypes.c_int
@@ -209,17 +201,6 @@ def partition_size(head_size: int) -> int:
 def device_status() -> None:
     """Synchronises the current device and raises if a kernel gave up a bounded wait."""
     check(load_library().pa_device_status())
-
-
-def measure_read_bandwidth(ptr: int, nbytes: int, iters: int = 10, stream: int = 0,
-                           ptr2: int = 0, nbytes2: int = 0, method: int = 0) -> float:
-    """GB/s of a kernel that only reads `nbytes` at `ptr` (+ `nbytes2` at `ptr2`), blocking.
-    method 0: 16-byte loads; method 1: bulk copies into a shared-memory ring."""
-    rate = ctypes.c_float(0.0)
-    check(load_library().pa_measure_read_bandwidth(ctypes.c_void_p(ptr), nbytes, ctypes.c_void_p(ptr2 or None),
-                                                   nbytes2, method, iters, ctypes.c_void_p(stream),
-                                                   ctypes.byref(rate)))
-    return float(rate.value)
 
 
 def launch(entry: str, params: PaParams, stream: int, timed: bool) -> list[float]:

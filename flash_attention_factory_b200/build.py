@@ -1,4 +1,5 @@
-"""Builds libpaged_attention_b200.so in-tree with nvcc for sm_100a.
+"""Builds libpaged_attention_b200.so (the product) and libpaged_attention_b200_test_aids.so
+(test and measurement aids) in-tree with nvcc for sm_100a.
 
 Usage: ``python -m flash_attention_factory_b200.build [--force] [--verbose]``.
 The library is plain CUDA C++ behind a C ABI (include/paged_attention_b200.h);
@@ -21,8 +22,10 @@ CSRC = PKG_DIR / "csrc"
 INCLUDE = REPO_ROOT / "include"
 BUILD_DIR = PKG_DIR / "build"
 LIB_PATH = PKG_DIR / "libpaged_attention_b200.so"
+AIDS_LIB_PATH = PKG_DIR / "libpaged_attention_b200_test_aids.so"
 
 SOURCES = [
+    "host_common.cu",
     "c_api.cu",
     "launch_kernels_loop.cu",
     "launch_kernels_reduce.cu",
@@ -30,6 +33,8 @@ SOURCES = [
     "launch_kernels_fp8_reduce.cu",
     "cache_write.cu",
 ]
+# the aid library links its own copy of the shared host pieces and nothing of the product
+AIDS_SOURCES = ["host_common.cu", "test_aids.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -51,10 +56,10 @@ def _newest_mtime(paths) -> float:
 
 
 def needs_build() -> bool:
-    if not LIB_PATH.exists():
+    if not LIB_PATH.exists() or not AIDS_LIB_PATH.exists():
         return True
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h*"))
-    return _newest_mtime(deps) > LIB_PATH.stat().st_mtime
+    return _newest_mtime(deps) > min(LIB_PATH.stat().st_mtime, AIDS_LIB_PATH.stat().st_mtime)
 
 
 def _compile_one(nvcc: str, src: str, verbose: bool) -> Path:
@@ -77,13 +82,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         return LIB_PATH
     nvcc = find_nvcc()
     BUILD_DIR.mkdir(exist_ok=True)
-    with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
-        objs = list(pool.map(lambda s: _compile_one(nvcc, s, verbose), SOURCES))
-    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
-            "-o", str(LIB_PATH), *map(str, objs)]
-    res = subprocess.run(link, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    every = list(dict.fromkeys(SOURCES + AIDS_SOURCES))
+    with concurrent.futures.ThreadPoolExecutor(max_workers=len(every)) as pool:
+        objs = dict(zip(every, pool.map(lambda s: _compile_one(nvcc, s, verbose), every)))
+    for target, sources in ((LIB_PATH, SOURCES), (AIDS_LIB_PATH, AIDS_SOURCES)):
+        link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
+                "-o", str(target), *(str(objs[s]) for s in sources)]
+        res = subprocess.run(link, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
     return LIB_PATH
 
 

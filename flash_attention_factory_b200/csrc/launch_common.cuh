@@ -19,8 +19,9 @@
 namespace pa {
 
 // ------------------------------------------------------------------ errors
-void set_last_error(const char *fmt, ...); // defined in c_api.cu
+void set_last_error(const char *fmt, ...); // defined in host_common.cu
 int fail(int code, const char *fmt, ...);  // sets the message, returns code
+const char *last_error();                  // message of the last failure on this thread
 
 #define PA_CUDA_TRY(expr)                                                               \
   do {                                                                                  \
@@ -34,7 +35,7 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_
                                    const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                    const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn get_encode_tiled(); // defined in c_api.cu; nullptr if the driver lacks it
+EncodeTiledFn get_encode_tiled(); // defined in host_common.cu; nullptr if the driver lacks it
 
 // Describes one cache tensor to the TMA unit as (head dim, token row, KV head): extents
 // (head_size, num_blocks*block_size, num_kv_heads), strides (1 elem, num_kv_heads*head_size
@@ -56,11 +57,16 @@ int encode_cache_map(CUtensorMap *map, const void *cache, const pa_params *p, ui
       (KV == KV_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const CUtensorMapSwizzle sw =
       (geo::slab_bytes == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-  // debugging knob: PA_TMA_L2_PROMOTION=0..3 (none, 64 B, 128 B, 256 B); default 256 B
+  // 256-byte L2 promotion measured best; a -DPA_TUNING_KNOBS build reads
+  // PA_TMA_L2_PROMOTION=0..3 (none, 64 B, 128 B, 256 B) instead
+#ifdef PA_TUNING_KNOBS
   static const int promo = [] {
     const char *e = std::getenv("PA_TMA_L2_PROMOTION");
     return (e != nullptr && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 3;
   }();
+#else
+  constexpr int promo = 3;
+#endif
   const CUtensorMapL2promotion l2 = promo == 0   ? CU_TENSOR_MAP_L2_PROMOTION_NONE
                                     : promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
                                     : promo == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
@@ -131,18 +137,20 @@ struct DeviceInfo {
   int sm_count;
   int cc_major;
 };
-int get_device_info(DeviceInfo *info); // cached per device; defined in c_api.cu
+int get_device_info(DeviceInfo *info); // cached per device; defined in host_common.cu
 
 // Cluster size of the loop variant: enough CTAs to give every SM two, using
 // only what the host knows (num_seqs, num_kv_heads and the context-length hint).
 inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_count, uint32_t tokens_per_stage) {
-  // debugging knob: PA_LOOP_CLUSTER=1..8 forces the cluster size
+#ifdef PA_TUNING_KNOBS
+  // tuning build only: PA_LOOP_CLUSTER=1..8 forces the cluster size
   static const int forced = [] {
     const char *e = std::getenv("PA_LOOP_CLUSTER");
     const int v = e ? std::atoi(e) : 0;
     return (v >= 1 && v <= 8) ? v : 0;
   }();
   if (forced != 0) return static_cast<uint32_t>(forced);
+#endif
   const uint64_t units = static_cast<uint64_t>(p->num_seqs) * (p->num_kv_heads / hpc);
   const uint64_t want = 2ull * static_cast<uint64_t>(sm_count);
   uint32_t cs = 1;
@@ -155,6 +163,12 @@ inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_cou
     while (cs > 1 && stages / cs < 8) cs /= 2;
   }
   return cs;
+}
+
+// Longest context a sequence's block-table row can address, saturated to 32 bits.
+inline uint32_t context_limit(const pa_params *p) {
+  const uint64_t tokens = static_cast<uint64_t>(p->max_blocks_per_seq) * p->block_size;
+  return tokens > 0xffffffffull ? 0xffffffffu : static_cast<uint32_t>(tokens);
 }
 
 template <int D, int KV, int NWARPS = 4>
@@ -176,18 +190,22 @@ AttnArgs make_attn_args(const pa_params *p, bool loop_mode = false, int sm_count
   a.max_blocks_per_seq = p->max_blocks_per_seq;
   a.max_num_partitions = p->max_num_partitions;
   a.block_shift = log2_pow2(p->block_size);
+  a.ctx_limit = context_limit(p);
   // KV heads per CTA: with 4 a warp owns a head and nothing is merged across warps
   a.hpc = (p->num_kv_heads % 4 == 0) ? 4u : ((p->num_kv_heads % 2 == 0) ? 2u : 1u);
   if (NWARPS == 8) {
     a.hpc = 8u; // the wide CTA is only chosen for num_kv_heads % 8 == 0: a warp per head
-  } else {
-    // debugging knob: PA_FORCE_HPC=1|2 lowers the number of KV heads per CTA
+  }
+#ifdef PA_TUNING_KNOBS
+  else {
+    // tuning build only: PA_FORCE_HPC=1|2 lowers the number of KV heads per CTA
     static const int forced = [] {
       const char *e = std::getenv("PA_FORCE_HPC");
       return e ? std::atoi(e) : 0;
     }();
     if ((forced == 1 || forced == 2) && static_cast<uint32_t>(forced) < a.hpc) a.hpc = forced;
   }
+#endif
   // The loop variant has one cluster of at most 8 CTAs per (sequence, head group): with very
   // few sequences, fewer heads per CTA (warps then split the tokens of a head) is the only
   // way to put a CTA on every SM
@@ -226,8 +244,10 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
 
   AttnArgs args = make_attn_args<D, KV, NWARPS>(p, MODE == MODE_LOOP, dev.sm_count);
   if (MODE == MODE_SPLIT) {
-    static std::atomic<uint32_t> next_slot{0}; // per kernel instantiation, like its counters
-    args.sched_slot = next_slot.fetch_add(1, std::memory_order_relaxed) % kSchedSlots;
+    // one allocator per translation unit, like the counter table it indexes
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    PA_CUDA_TRY(cudaStreamIsCapturing(stream, &capture));
+    args.sched_slot = next_sched_slot(capture != cudaStreamCaptureStatusNone);
   }
   CUtensorMap map_k, map_v;
   if (int rc = encode_cache_map<D, KV>(&map_k, p->key_cache, p, args.rows_per_box, args.heads_per_box)) return rc;
@@ -309,14 +329,15 @@ int enqueue_merge(const pa_params *p, cudaStream_t stream) {
                                    static_cast<const __half *>(p->tmp_out),
                                    static_cast<const float *>(p->max_logits),
                                    static_cast<const float *>(p->exp_sums), p->context_lens, p->seq_indices,
-                                   p->num_heads, static_cast<uint32_t>(pairs), p->max_num_partitions, psize));
+                                   p->num_heads, static_cast<uint32_t>(pairs), p->max_num_partitions, psize,
+                                   context_limit(p)));
     return PA_OK;
   }
   PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partitions_kernel<D>, static_cast<__half *>(p->out),
                                  static_cast<const __half *>(p->tmp_out),
                                  static_cast<const float *>(p->max_logits),
                                  static_cast<const float *>(p->exp_sums), p->context_lens, p->seq_indices,
-                                 p->num_heads, p->max_num_partitions, psize));
+                                 p->num_heads, p->max_num_partitions, psize, context_limit(p)));
   return PA_OK;
 }
 

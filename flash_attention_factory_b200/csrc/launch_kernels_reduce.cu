@@ -65,7 +65,13 @@ int static_scratch_base(unsigned char **base) {
 extern "C" PA_API int launch_kernels_reduce_static_scratch(const pa_params *p, void *stream) {
   using namespace pa;
   if (p == nullptr) return fail(PA_ERR_BAD_ARG, "params is null");
-  // size check first: it needs nothing from the device
+  // A subset launch indexes the scratch rows by the sequence ids in a device array this call
+  // cannot read; the array built into the library only has room for ids below num_seqs, so the
+  // library refuses what it cannot bound.
+  if (p->seq_indices != nullptr)
+    return fail(PA_ERR_BAD_ARG, "the static-scratch entry point does not take seq_indices: scratch rows are "
+                                "indexed by sequence id and the built-in array is sized from num_seqs");
+  // size check next: it needs nothing from the device
   const size_t rows = static_cast<size_t>(p->num_seqs) * p->num_heads * p->max_num_partitions;
   const size_t stats_bytes = align256(rows * sizeof(float));
   const size_t partial_bytes = align256(rows * p->head_size * sizeof(__half));

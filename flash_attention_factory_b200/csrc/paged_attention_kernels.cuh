@@ -33,6 +33,8 @@
 // (pa::mbar_wait_bounded).
 #pragma once
 
+#include <atomic>
+
 #include <cooperative_groups.h>
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -50,11 +52,28 @@ enum Mode : int { MODE_LOOP = 0, MODE_SPLIT = 1 };
 static __device__ int g_pa_device_status = 0;
 
 // Work counters of the split kernel's dynamic scheduler: [slot][0] hands out item numbers,
-// [slot][1] counts retired CTAs; the last CTA of a launch zeroes its slot again.  The host
-// gives consecutive launches consecutive slots, so launches that overlap in time (other
-// streams, programmatic dependent launch) never share one.
+// [slot][1] counts retired CTAs; the last CTA of a launch zeroes its slot again.  The table
+// exists once per translation unit and is shared by every kernel instantiation of that unit,
+// so the unit also has exactly one slot allocator (next_sched_slot below): consecutive
+// launches of the unit, whatever their instantiation and stream, take consecutive slots, and
+// launches that overlap in time (other streams, programmatic dependent launch) never share
+// one unless more than kDirectSchedSlots of them are in flight at once.  A launch recorded
+// into a CUDA graph keeps its slot for every replay, so recorded launches draw from a range of
+// their own (the upper half of the table) that direct launches never touch; two replays of one
+// graph never overlap, and different recordings hold different slots (up to kSchedSlots -
+// kDirectSchedSlots recorded launches per unit before the range wraps).
 constexpr uint32_t kSchedSlots = 1024;
+constexpr uint32_t kDirectSchedSlots = 512;
 static __device__ unsigned int g_sched[kSchedSlots][2];
+static std::atomic<uint32_t> g_next_direct_slot{0};
+static std::atomic<uint32_t> g_next_captured_slot{0};
+
+inline uint32_t next_sched_slot(bool capturing) {
+  if (capturing)
+    return kDirectSchedSlots +
+           g_next_captured_slot.fetch_add(1, std::memory_order_relaxed) % (kSchedSlots - kDirectSchedSlots);
+  return g_next_direct_slot.fetch_add(1, std::memory_order_relaxed) % kDirectSchedSlots;
+}
 
 struct AttnArgs {
   const __half *query;
@@ -85,6 +104,9 @@ struct AttnArgs {
   const float *v_scale_per_head;
   float sm_scale_log2;       // sm_scale * log2(e)
   uint32_t sched_slot;       // row of g_sched this launch uses (split mode)
+  // max_blocks_per_seq * block_size (saturated to 32 bits): a context length beyond it is cut
+  // to it, so no block-table read leaves the sequence's row whatever context_lens holds
+  uint32_t ctx_limit;
   // optional list of the sequences this launch covers (num_seqs entries); all tensors are
   // still indexed by the sequence ids found in the list
   const uint32_t *seq_indices;
@@ -179,7 +201,7 @@ struct SplitCursor {
   __device__ __forceinline__ void load_window(const AttnArgs &args, uint32_t groups, uint32_t lane) {
     const uint32_t pos = window_seq + lane;
     lane_seq = (pos < args.num_seqs) ? (args.seq_indices != nullptr ? __ldg(args.seq_indices + pos) : pos) : 0u;
-    lane_ctx = (pos < args.num_seqs) ? __ldg(args.context_lens + lane_seq) : 0u;
+    lane_ctx = (pos < args.num_seqs) ? min(__ldg(args.context_lens + lane_seq), args.ctx_limit) : 0u;
     const uint32_t parts = min(divide_round_up(lane_ctx, PARTITION), args.max_num_partitions);
     uint32_t v = parts * groups;
 #pragma unroll
@@ -374,7 +396,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     first.seq = (args.seq_indices != nullptr) ? __ldg(args.seq_indices + position) : position;
     first.head_base = blockIdx.y * hpc;
     first.partition = 0;
-    const uint32_t ctx = args.context_lens[first.seq];
+    const uint32_t ctx = min(args.context_lens[first.seq], args.ctx_limit);
     // the context is cut into whole stages, spread evenly over the CTAs of the cluster
     const uint32_t total_stages = divide_round_up(ctx, tps);
     const uint32_t stages_per_rank = divide_round_up(total_stages, num_ranks);
@@ -1108,7 +1130,8 @@ __global__ void __launch_bounds__(128)
 merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp_out,
                         const float *__restrict__ max_logits, const float *__restrict__ exp_sums,
                         const uint32_t *__restrict__ context_lens, const uint32_t *__restrict__ seq_indices,
-                        uint32_t num_heads, uint32_t max_num_partitions, uint32_t partition_size) {
+                        uint32_t num_heads, uint32_t max_num_partitions, uint32_t partition_size,
+                        uint32_t ctx_limit) {
   constexpr uint32_t LANES_PER_ROW = D / 4;         // each lane owns 4 dims (8 bytes)
   constexpr uint32_t ROWS = 128 / LANES_PER_ROW;    // partitions handled in parallel
   constexpr uint32_t UNROLL = 4;                    // rows in flight per thread
@@ -1120,7 +1143,7 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
   // kernel drains; nothing is read before that kernel has completed and its writes are visible.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const uint32_t ctx = context_lens[seq];
+  const uint32_t ctx = min(context_lens[seq], ctx_limit); // cut like the attention kernel cuts it
   const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
   const size_t base = (static_cast<size_t>(seq) * num_heads + head) * max_num_partitions;
   __half *orow = out + (static_cast<size_t>(seq) * num_heads + head) * D;
@@ -1217,7 +1240,8 @@ merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict_
                              const float *__restrict__ max_logits, const float *__restrict__ exp_sums,
                              const uint32_t *__restrict__ context_lens,
                              const uint32_t *__restrict__ seq_indices, uint32_t num_heads,
-                             uint32_t num_pairs, uint32_t max_num_partitions, uint32_t partition_size) {
+                             uint32_t num_pairs, uint32_t max_num_partitions, uint32_t partition_size,
+                             uint32_t ctx_limit) {
   constexpr uint32_t DPL = D / 32;          // dims per lane: 4 or 2
   constexpr uint32_t ROWS = 128 / (D / 4);  // residue classes of the CTA-per-pair kernel
   const uint32_t lane = threadIdx.x & 31u;
@@ -1228,7 +1252,7 @@ merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict_
   const uint32_t pos = work / num_heads;
   const uint32_t seq = (seq_indices != nullptr) ? __ldg(seq_indices + pos) : pos;
   const uint32_t pair = seq * num_heads + (work - pos * num_heads); // seq * num_heads + head
-  const uint32_t ctx = context_lens[seq];
+  const uint32_t ctx = min(context_lens[seq], ctx_limit);
   const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
   const size_t base = static_cast<size_t>(pair) * max_num_partitions;
   const __half *rows = tmp_out + base * D + lane * DPL;

@@ -92,9 +92,14 @@ class BoundStep:
             self.host_step.host_out = io.out_host.data_ptr()
             self.host_step.out_bytes = io.d2h_bytes
         self._fn = _cabi.load_library().pa_decode_step_host
+        self._device_index = io.device.index if io.device.index is not None else torch.cuda.current_device()
 
     def run(self, synchronize: bool = True) -> torch.Tensor:
         """Upload, launch, download (and wait) on the current stream; returns the host result."""
+        # the library reads the current device (SM count, kernel attributes, cached tables)
+        if torch.cuda.current_device() != self._device_index:
+            with torch.cuda.device(self.io.device):
+                return self.run(synchronize)
         stream = torch.cuda.current_stream(self.io.device).cuda_stream
         rc = self._fn(self.entry, ctypes.byref(self.params), ctypes.byref(self.host_step),
                       ctypes.c_void_p(stream), 1 if synchronize else 0)

@@ -12,7 +12,10 @@
  *
  * Memory contract (same as the reference): every buffer is allocated and owned
  * by the caller and lives on the current CUDA device; the library allocates
- * nothing on the device and keeps no per-call state.
+ * nothing on the device.  The only state it keeps between calls is a table of
+ * work counters inside its device image, of which every split-context launch
+ * takes a row of its own and hands it back zeroed (see INTEGRATION.md on
+ * overlapping launches and CUDA graphs).
  *
  * Data layouts (reference paged_attention_kernel_loop.hpp:44-62):
  *   query        fp16  [num_seqs, num_heads, head_size]
@@ -179,7 +182,10 @@ PA_API int launch_kernels_fp8_reduce(const pa_params *p, void *stream, float *us
  * cover ceil(max context / partition size).  The call fails with
  * PA_ERR_BAD_ARG, before any work is enqueued, if
  *   2 * align256(4 * rows) + align256(2 * head_size * rows) > PA_STATIC_SCRATCH_BYTES,
- *   rows = num_seqs * num_heads * max_num_partitions.
+ *   rows = num_seqs * num_heads * max_num_partitions,
+ * or if p->seq_indices is not NULL: a subset launch addresses scratch rows by
+ * sequence id, ids the host cannot see, so the fixed array cannot be sized for
+ * it (use launch_kernels_reduce with caller scratch for subset launches).
  *
  * The first call on each device looks up the array's device address (with
  * that device current) and caches it; make that first call outside of any
@@ -257,25 +263,6 @@ PA_API const char *pa_last_error(void);
  * kernel of this library ever gave up a bounded wait, else PA_ERR_TIMEOUT.
  * Synchronises the device. */
 PA_API int pa_device_status(void);
-
-/* Self-test of the failure path (test hook; allocates 4 bytes of device memory and
- * synchronises): launches one CTA that waits on a barrier nothing ever completes, with the
- * given limit.  Returns PA_OK if the wait gave up within the limit; afterwards
- * pa_device_status() reports PA_ERR_TIMEOUT once, exactly as it would after a real
- * time-out in an attention kernel. */
-PA_API int pa_selftest_wait_timeout(uint32_t limit_us);
-
-/* Measurement aid, no counterpart in the reference: times `iters` launches of a kernel that
- * only reads, with CUDA events on `stream`, and stores the read rate in GB/s.  One launch reads
- * `bytes` at `buf` and then, if `buf2` is not NULL, `bytes2` at `buf2` (both 16-byte aligned)
- * -- e.g. the K pool and the V pool, so that the figure is for the same byte count in one
- * launch as the attention kernel reads.  method 0: 16-byte loads with a grid stride, folded
- * into a checksum; method 1: 16 KB bulk copies into a shared-memory ring (the copy engine the
- * attention kernels use), data never looked at, whole 16 KB chunks only.  Blocks until done;
- * allocates 4 bytes of device memory.  With buffers much larger than L2 this is the HBM read
- * rate a kernel that does nothing but read reaches at that size. */
-PA_API int pa_measure_read_bandwidth(const void *buf, uint64_t bytes, const void *buf2, uint64_t bytes2,
-                                     uint32_t method, uint32_t iters, void *stream, float *gb_per_s);
 
 /* Library version, "major.minor". */
 PA_API const char *pa_version(void);

@@ -20,20 +20,57 @@ def lib():
     return pkg.load_library()
 
 
-def declared_symbols():
-    names = []
-    for header in (ROOT / "include").glob("*.h"):
-        text = header.read_text()
-        names += re.findall(r"PA_API\s+[\w\s\*]+?\b(\w+)\s*\(", text)
-    return sorted(set(names))
+def declared_symbols(header_name):
+    text = (ROOT / "include" / header_name).read_text()
+    return sorted(set(re.findall(r"PA_API\s+[\w\s\*]+?\b(\w+)\s*\(", text)))
 
 
 def test_header_symbols_are_exported(lib):
-    names = declared_symbols()
-    assert set(_cabi.EXPORTED_SYMBOLS) <= set(names)
+    from flash_attention_factory_b200 import _test_aids
+
+    # every header under include/ belongs to one of the two libraries
+    assert sorted(h.name for h in (ROOT / "include").glob("*.h")) == [
+        "paged_attention_b200.h", "paged_attention_b200_test_aids.h"]
+    names = declared_symbols("paged_attention_b200.h")
+    assert set(_cabi.EXPORTED_SYMBOLS) == set(names)
     assert len(names) >= 9
     for name in names:
         assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+    aid_names = declared_symbols("paged_attention_b200_test_aids.h")
+    assert set(_test_aids.EXPORTED_SYMBOLS) == set(aid_names)
+    aids = _test_aids.load_library()
+    for name in aid_names:
+        assert hasattr(aids, name), f"{name} declared in the aid header but not exported"
+    # the product library carries no test aid, and allocates nothing: it imports no allocator
+    for name in aid_names + ["pa_selftest_wait_timeout", "pa_measure_read_bandwidth"]:
+        assert not hasattr(lib, name), f"{name} must not be exported by the product library"
+
+
+def test_public_header_is_plain_c(tmp_path):
+    """include/paged_attention_b200.h compiles as C99 and the struct layout matches ctypes."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler on this machine")
+    src = tmp_path / "abi_check.c"
+    src.write_text(
+        '#include <stddef.h>\n#include <stdio.h>\n#include "paged_attention_b200.h"\n'
+        '#include "paged_attention_b200_test_aids.h"\n'
+        "int main(void) {\n"
+        "  pa_params p = {0};\n  pa_host_step io = {0};\n  pa_cache_write_params c = {0};\n"
+        "  (void)io; (void)c; p.kv_dtype = PA_KV_FP8_E4M3;\n"
+        '  printf("%zu %zu %zu %zu %zu\\n", sizeof(pa_params), offsetof(pa_params, num_blocks),\n'
+        "         offsetof(pa_params, sm_scale), sizeof(pa_host_step), sizeof(pa_cache_write_params));\n"
+        "  return p.kv_dtype == 2 ? 0 : 1;\n}\n")
+    exe = tmp_path / "abi_check"
+    subprocess.run([gcc, "-std=c99", "-pedantic", "-Wall", "-Werror", f"-I{ROOT / 'include'}", str(src), "-o", str(exe)],
+                   check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert [int(x) for x in out] == [
+        ctypes.sizeof(_cabi.PaParams), _cabi.PaParams.num_blocks.offset, _cabi.PaParams.sm_scale.offset,
+        ctypes.sizeof(_cabi.PaHostStep), ctypes.sizeof(_cabi.PaCacheWriteParams)]
 
 
 def test_params_struct_matches_header_layout():
@@ -171,3 +208,18 @@ def test_cache_write_validates_on_the_host(lib):
     assert call(fp8_scale=0.0)[0] == _cabi.PA_ERR_BAD_ARG
     assert call(key_cache=0x3004)[0] == _cabi.PA_ERR_BAD_ARG
     assert lib.pa_reshape_and_cache(None, None) == _cabi.PA_ERR_BAD_ARG
+
+
+def test_static_scratch_refusals_need_no_gpu(lib):
+    """The no-allocation entry point decides both refusals on the host, before any CUDA call."""
+    p = _cabi.PaParams()
+    p.num_seqs, p.num_heads, p.head_size, p.num_kv_heads, p.max_num_partitions = 2, 8, 128, 2, 4
+    p.max_blocks_per_seq, p.block_size, p.num_queries_per_tokens = 128, 16, 4
+    p.num_blocks, p.sm_scale, p.kv_dtype = 1 << 12, 0.1, _cabi.KV_F16
+    p.seq_indices = 0x1000  # never dereferenced
+    assert lib.launch_kernels_reduce_static_scratch(ctypes.byref(p), None) == _cabi.PA_ERR_BAD_ARG
+    assert "seq_indices" in lib.pa_last_error().decode()
+    p.seq_indices = None
+    p.num_seqs, p.num_heads, p.num_kv_heads, p.num_queries_per_tokens, p.max_num_partitions = 3259, 3, 3, 1, 13
+    assert lib.launch_kernels_reduce_static_scratch(ctypes.byref(p), None) == _cabi.PA_ERR_BAD_ARG
+    assert "static scratch too small" in lib.pa_last_error().decode()

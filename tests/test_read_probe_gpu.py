@@ -7,7 +7,7 @@ pytestmark = pytest.mark.gpu
 def test_read_probe_reports_a_rate_and_leaves_the_buffer_alone(cuda_device):
     import torch
 
-    from flash_attention_factory_b200 import _cabi
+    from flash_attention_factory_b200 import _test_aids as _cabi
 
     with torch.cuda.device(cuda_device):
         buf = torch.randint(0, 255, (512 * 2**20 + 48,), dtype=torch.uint8, device=cuda_device)

@@ -4,8 +4,11 @@ Some callers of this library have no allocator to offer: their device memory bel
 pool they do not control, or allocation is off limits once serving has started.  The entry
 point keeps the per-partition scratch in an array built into the library instead.  This
 test drives it through the C ABI (ctypes, no scratch tensors passed) and compares it with
-launch_kernels_reduce on the same inputs, twice in a row with different shapes so that the
-second call runs over whatever the first one left in the shared array.
+launch_kernels_reduce on the same inputs -- same kernels, fixed summation order, so the bits
+must be equal -- and with the CPU oracle, twice in a row with different shapes so that the
+second call runs over whatever the first one left in the shared array.  Further cases: the
+largest problem the array holds (accepted, right answers) and one row more (refused), and a
+subset launch (refused: its scratch rows are addressed by sequence ids the host cannot see).
 
 The file sorts last on purpose: a run that stops at the first failure has then already
 executed every other test.
@@ -16,11 +19,12 @@ import pytest
 import torch
 
 from _util import ATOL, RTOL, assert_close, make_case, run_entry
+from oracle import paged_attention_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 
 
-def _run_static(case, device):
+def _run_static(case, device, npart=None):
     """Calls the no-allocation entry point directly over the C ABI; returns `out` on the CPU."""
     import flash_attention_factory_b200 as pkg
     from flash_attention_factory_b200 import _cabi
@@ -35,7 +39,7 @@ def _run_static(case, device):
     s, h, d = q.shape
     psize = pkg.partition_size(d)
     max_ctx = int(case["context_lens"].max())
-    npart = max(1, (max_ctx + psize - 1) // psize)
+    npart = npart or max(1, (max_ctx + psize - 1) // psize)
     out = torch.full((s, h, d), float("nan"), dtype=torch.float16, device=device)
     p = _cabi.PaParams()
     p.out, p.query = out.data_ptr(), q.data_ptr()
@@ -67,9 +71,74 @@ def test_static_scratch_matches_the_allocating_entry_point_twice_in_a_row(cuda_d
     second = make_case(seed=72, num_seqs=2, num_heads=12, num_kv_heads=4, head_size=64, block_size=64,
                        context_lens=[300, 2100])
     for case in (first, second):
-        want = run_entry("reduce", case, cuda_device)["out"]
+        same_kernels = run_entry("reduce", case, cuda_device)["out"]
         got = _run_static(case, cuda_device)
-        assert_close(got, want, atol=ATOL, rtol=RTOL, what="static scratch vs launch_kernels_reduce")
+        assert torch.equal(got, same_kernels), "static scratch must give the bits of launch_kernels_reduce"
+        want = oracle.paged_attention_ref(case["query"], case["key_cache"], case["value_cache"],
+                                          case["block_tables"], case["context_lens"], sm_scale=case["sm_scale"],
+                                          sinks=case.get("sinks"))
+        assert_close(got, want, atol=ATOL, rtol=RTOL, what="static scratch vs oracle")
+
+
+def _shared_pool_case(seed, num_seqs, num_heads, num_kv_heads, context_lens, pool_blocks=4096):
+    """Many sequences over one small pool of blocks (rows of the table may name the same
+    physical block: attention only reads), so that a batch of a thousand sequences stays small."""
+    g = torch.Generator().manual_seed(seed)
+    ctx = torch.as_tensor(context_lens, dtype=torch.int32)
+    mb = (int(ctx.max()) + 15) // 16
+    return dict(query=torch.randn(num_seqs, num_heads, 128, generator=g).to(torch.float16),
+                key_cache=torch.randn(pool_blocks, 16, num_kv_heads, 128, generator=g).to(torch.float16),
+                value_cache=torch.randn(pool_blocks, 16, num_kv_heads, 128, generator=g).to(torch.float16),
+                block_tables=torch.randint(0, pool_blocks, (num_seqs, mb), generator=g, dtype=torch.int32),
+                context_lens=ctx, sinks=None, sm_scale=128 ** -0.5, fp8_scale=1.0, kv_dtype="float16",
+                block_size=16)
+
+
+def test_static_scratch_at_its_capacity(cuda_device):
+    """rows = num_seqs * num_heads * max_num_partitions = 127100 with head size 128 needs
+    2 * align256(4 * rows) + 256 * rows = 33554432 bytes, exactly the array; 127101 rows do not fit."""
+    import flash_attention_factory_b200 as pkg
+    from flash_attention_factory_b200 import _cabi
+
+    s, h, npart = 1271, 4, 25
+    assert 2 * ((4 * s * h * npart + 255) // 256 * 256) + 256 * s * h * npart == _cabi.STATIC_SCRATCH_BYTES
+    g = torch.Generator().manual_seed(5)
+    ctx = torch.randint(1, 700, (s,), generator=g).tolist()
+    ctx[0], ctx[s // 2], ctx[-1] = 25 * 512, 25 * 512 - 1, 24 * 512 + 1  # the last partition row is in use
+    case = _shared_pool_case(seed=6, num_seqs=s, num_heads=h, num_kv_heads=2, context_lens=ctx)
+    got = _run_static(case, cuda_device, npart=npart)
+    same_kernels = run_entry("reduce", case, cuda_device, max_num_partitions=npart)["out"]
+    assert torch.equal(got, same_kernels)
+    sample = [0, 1, 2, s // 2, s - 2, s - 1]
+    want = oracle.paged_attention_ref(case["query"][sample], case["key_cache"], case["value_cache"],
+                                      case["block_tables"][sample], case["context_lens"][sample],
+                                      sm_scale=case["sm_scale"])
+    assert_close(got[sample], want, atol=ATOL, rtol=RTOL, what="static scratch at capacity vs oracle")
+    # one row more: 127101 = 3259 * 3 * 13
+    lib = pkg.load_library()
+    p = _cabi.PaParams()
+    p.num_seqs, p.num_heads, p.head_size, p.num_kv_heads, p.max_num_partitions = 3259, 3, 128, 3, 13
+    p.max_blocks_per_seq, p.block_size, p.num_queries_per_tokens = 512, 16, 1
+    p.num_blocks, p.sm_scale, p.kv_dtype = 1 << 12, 0.1, _cabi.KV_F16
+    assert lib.launch_kernels_reduce_static_scratch(ctypes.byref(p), None) == _cabi.PA_ERR_BAD_ARG
+    assert "127101 rows" in lib.pa_last_error().decode()
+
+
+def test_static_scratch_refuses_subset_launches(cuda_device):
+    """With seq_indices the kernels address scratch rows by sequence id; the library cannot
+    bound ids it cannot read, so the fixed array is not offered to subset launches."""
+    import flash_attention_factory_b200 as pkg
+    from flash_attention_factory_b200 import _cabi
+
+    lib = pkg.load_library()
+    ids = torch.tensor([5, 9], dtype=torch.int32, device=cuda_device)
+    p = _cabi.PaParams()
+    p.num_seqs, p.num_heads, p.head_size, p.num_kv_heads, p.max_num_partitions = 2, 8, 128, 2, 4
+    p.max_blocks_per_seq, p.block_size, p.num_queries_per_tokens = 128, 16, 4
+    p.num_blocks, p.sm_scale, p.kv_dtype = 1 << 12, 0.1, _cabi.KV_F16
+    p.seq_indices = ids.data_ptr()
+    assert lib.launch_kernels_reduce_static_scratch(ctypes.byref(p), None) == _cabi.PA_ERR_BAD_ARG
+    assert "seq_indices" in lib.pa_last_error().decode()
 
 
 def test_static_scratch_rejects_problems_beyond_its_capacity(cuda_device):
