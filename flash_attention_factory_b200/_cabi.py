@@ -36,6 +36,8 @@ EXPORTED_SYMBOLS = (
     "pa_last_error",
     "pa_device_status",
     "pa_decode_step_host",
+    "pa_decode_step_host_batch",
+    "pa_split_by_kv_length",
     "pa_version",
 )
 
@@ -75,6 +77,7 @@ class PaParams(ctypes.Structure):
         ("softcap", ctypes.c_float),
         ("reserved2", ctypes.c_float),
         ("seq_indices", ctypes.c_void_p),
+        ("block_table_offsets", ctypes.c_void_p),
     ]
 
 
@@ -126,6 +129,22 @@ class PaHostStep(ctypes.Structure):
     ]
 
 
+class PaHostBatch(ctypes.Structure):
+    """struct pa_host_batch of include/paged_attention_b200.h."""
+
+    _fields_ = [
+        ("host_query", ctypes.c_void_p),
+        ("host_block_tables", ctypes.c_void_p),
+        ("host_block_table_offsets", ctypes.c_void_p),
+        ("host_context_lens", ctypes.c_void_p),
+        ("host_out", ctypes.c_void_p),
+        ("sub_batches", ctypes.c_uint32),
+        ("flags", ctypes.c_uint32),
+    ]
+
+
+STEP_LAST_OUT_DIRECT = 1
+
 ENTRY_IDS = {"launch_kernels_loop": 0, "launch_kernels_reduce": 1, "launch_kernels_fp8_loop": 2,
              "launch_kernels_fp8_reduce": 3}
 
@@ -168,6 +187,12 @@ def load_library() -> ctypes.CDLL:
     lib.pa_decode_step_host.argtypes = [ctypes.c_int32, ctypes.POINTER(PaParams), ctypes.POINTER(PaHostStep),
                                         ctypes.c_void_p, ctypes.c_int32]
     lib.pa_decode_step_host.restype = ctypes.c_int
+    lib.pa_decode_step_host_batch.argtypes = [ctypes.c_int32, ctypes.POINTER(PaParams), ctypes.POINTER(PaHostBatch),
+                                              ctypes.c_void_p, ctypes.c_int32]
+    lib.pa_decode_step_host_batch.restype = ctypes.c_int
+    lib.pa_split_by_kv_length.argtypes = [ctypes.POINTER(ctypes.c_uint32), ctypes.c_uint32, ctypes.c_uint32,
+                                          ctypes.POINTER(ctypes.c_uint32)]
+    lib.pa_split_by_kv_length.restype = ctypes.c_int
     lib.pa_version.argtypes = []
     lib.pa_version.restype = ctypes.c_char_p
     _lib = lib
@@ -201,6 +226,15 @@ def partition_size(head_size: int) -> int:
 def device_status() -> None:
     """Synchronises the current device and raises if a kernel gave up a bounded wait."""
     check(load_library().pa_device_status())
+
+
+def split_by_kv_length(context_lens, parts: int) -> list[tuple[int, int]]:
+    """[lo, hi) ranges of consecutive sequences with equal shares of the KV tokens (pa_split_by_kv_length)."""
+    lens = [int(c) for c in context_lens]
+    arr = (ctypes.c_uint32 * max(1, len(lens)))(*lens)
+    bounds = (ctypes.c_uint32 * (parts + 1))()
+    check(load_library().pa_split_by_kv_length(arr, len(lens), parts, bounds))
+    return [(int(bounds[r]), int(bounds[r + 1])) for r in range(parts)]
 
 
 def launch(entry: str, params: PaParams, stream: int, timed: bool) -> list[float]:

@@ -27,6 +27,7 @@ AIDS_LIB_PATH = PKG_DIR / "libpaged_attention_b200_test_aids.so"
 SOURCES = [
     "host_common.cu",
     "c_api.cu",
+    "host_step.cu",
     "launch_kernels_loop.cu",
     "launch_kernels_reduce.cu",
     "launch_kernels_fp8_loop.cu",

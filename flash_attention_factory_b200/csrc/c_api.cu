@@ -50,30 +50,6 @@ PA_API int pa_query_policy(uint32_t head_size, uint32_t block_size, uint32_t gro
   return PA_OK;
 }
 
-PA_API int pa_decode_step_host(int32_t entry, const pa_params *p, const pa_host_step *io, void *stream,
-                               int32_t synchronize) {
-  if (p == nullptr || io == nullptr) return pa::fail(PA_ERR_BAD_ARG, "params or host step is null");
-  if (entry < PA_ENTRY_LOOP || entry > PA_ENTRY_FP8_REDUCE) return pa::fail(PA_ERR_BAD_ARG, "unknown entry %d", entry);
-  if ((io->in_bytes != 0 && (io->host_in == nullptr || io->dev_in == nullptr)) ||
-      (io->out_bytes != 0 && io->host_out == nullptr))
-    return pa::fail(PA_ERR_BAD_ARG, "host step: a buffer with a non-zero size is null");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (io->in_bytes != 0)
-    PA_CUDA_TRY(cudaMemcpyAsync(io->dev_in, io->host_in, io->in_bytes, cudaMemcpyHostToDevice, st));
-  int rc = PA_OK;
-  switch (entry) {
-  case PA_ENTRY_LOOP: rc = launch_kernels_loop(p, stream, nullptr); break;
-  case PA_ENTRY_REDUCE: rc = launch_kernels_reduce(p, stream, nullptr); break;
-  case PA_ENTRY_FP8_LOOP: rc = launch_kernels_fp8_loop(p, stream, nullptr); break;
-  default: rc = launch_kernels_fp8_reduce(p, stream, nullptr); break;
-  }
-  if (rc != PA_OK) return rc;
-  if (io->out_bytes != 0)
-    PA_CUDA_TRY(cudaMemcpyAsync(io->host_out, p->out, io->out_bytes, cudaMemcpyDeviceToHost, st));
-  if (synchronize != 0) PA_CUDA_TRY(cudaStreamSynchronize(st));
-  return PA_OK;
-}
-
 PA_API int pa_device_status(void) {
   cudaError_t err = cudaDeviceSynchronize();
   if (err != cudaSuccess) return pa::fail(PA_ERR_CUDA, "cudaDeviceSynchronize failed: %s", cudaGetErrorString(err));

@@ -108,7 +108,7 @@ inline int validate_params(const pa_params *p, bool fp8_entry, bool needs_scratc
   if (p->num_kv_heads == 0 || p->num_heads != p->num_kv_heads * p->num_queries_per_tokens)
     return fail(PA_ERR_BAD_ARG, "num_heads (%u) != num_kv_heads (%u) * num_queries_per_tokens (%u)",
                 p->num_heads, p->num_kv_heads, p->num_queries_per_tokens);
-  if (p->num_blocks == 0 || p->max_blocks_per_seq == 0)
+  if (p->num_blocks == 0 || (p->max_blocks_per_seq == 0 && p->block_table_offsets == nullptr))
     return fail(PA_ERR_BAD_ARG, "num_blocks and max_blocks_per_seq must be positive");
   if (p->num_blocks * p->block_size >= (1ull << 31))
     return fail(PA_ERR_BAD_ARG, "cache has too many token rows for a 32-bit TMA coordinate");
@@ -139,6 +139,16 @@ struct DeviceInfo {
 };
 int get_device_info(DeviceInfo *info); // cached per device; defined in host_common.cu
 
+// Longest context a sequence's block-table row can address, saturated to 32 bits.
+inline uint32_t context_limit(const pa_params *p) {
+  if (p->block_table_offsets != nullptr) return 0xffffffffu; // per sequence, known on the device only
+  const uint64_t tokens = static_cast<uint64_t>(p->max_blocks_per_seq) * p->block_size;
+  return tokens > 0xffffffffull ? 0xffffffffu : static_cast<uint32_t>(tokens);
+}
+
+// The caller's context-length hint, cut to what the block tables can address (0 = unknown).
+inline uint32_t context_hint(const pa_params *p) { return std::min(p->max_context_len, context_limit(p)); }
+
 // Cluster size of the loop variant: enough CTAs to give every SM two, using
 // only what the host knows (num_seqs, num_kv_heads and the context-length hint).
 inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_count, uint32_t tokens_per_stage) {
@@ -155,20 +165,14 @@ inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_cou
   const uint64_t want = 2ull * static_cast<uint64_t>(sm_count);
   uint32_t cs = 1;
   while (cs < 8 && units * cs < want) cs *= 2;
-  if (p->max_context_len != 0) {
+  if (context_hint(p) != 0) {
     // a CTA should own at least 8 stages of the longest context: below that the cluster merge
     // and the extra launches cost more than the split saves (config 1: 24 us unsplit, 36 us
     // with 8 CTAs per cluster)
-    const uint32_t stages = divide_round_up(p->max_context_len, tokens_per_stage);
+    const uint32_t stages = divide_round_up(context_hint(p), tokens_per_stage);
     while (cs > 1 && stages / cs < 8) cs /= 2;
   }
   return cs;
-}
-
-// Longest context a sequence's block-table row can address, saturated to 32 bits.
-inline uint32_t context_limit(const pa_params *p) {
-  const uint64_t tokens = static_cast<uint64_t>(p->max_blocks_per_seq) * p->block_size;
-  return tokens > 0xffffffffull ? 0xffffffffu : static_cast<uint32_t>(tokens);
 }
 
 template <int D, int KV, int NWARPS = 4>
@@ -191,6 +195,7 @@ AttnArgs make_attn_args(const pa_params *p, bool loop_mode = false, int sm_count
   a.max_num_partitions = p->max_num_partitions;
   a.block_shift = log2_pow2(p->block_size);
   a.ctx_limit = context_limit(p);
+  a.table_offsets = p->block_table_offsets;
   // KV heads per CTA: with 4 a warp owns a head and nothing is merged across warps
   a.hpc = (p->num_kv_heads % 4 == 0) ? 4u : ((p->num_kv_heads % 2 == 0) ? 2u : 1u);
   if (NWARPS == 8) {
@@ -285,7 +290,7 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
     const uint32_t cs = choose_cluster_size(p, args.hpc, dev.sm_count, args.tokens_per_stage);
     // the order in which clusters start only matters when they do not all fit at once
     const uint64_t ctas = static_cast<uint64_t>(cs) * (p->num_kv_heads / args.hpc) * p->num_seqs;
-    args.longest_first_hint = (ctas > 2ull * static_cast<uint64_t>(dev.sm_count)) ? p->max_context_len : 0u;
+    args.longest_first_hint = (ctas > 2ull * static_cast<uint64_t>(dev.sm_count)) ? context_hint(p) : 0u;
     cfg.gridDim = dim3(cs, p->num_kv_heads / args.hpc, p->num_seqs);
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = cs;
@@ -330,14 +335,15 @@ int enqueue_merge(const pa_params *p, cudaStream_t stream) {
                                    static_cast<const float *>(p->max_logits),
                                    static_cast<const float *>(p->exp_sums), p->context_lens, p->seq_indices,
                                    p->num_heads, static_cast<uint32_t>(pairs), p->max_num_partitions, psize,
-                                   context_limit(p)));
+                                   context_limit(p), p->block_table_offsets, log2_pow2(p->block_size)));
     return PA_OK;
   }
   PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partitions_kernel<D>, static_cast<__half *>(p->out),
                                  static_cast<const __half *>(p->tmp_out),
                                  static_cast<const float *>(p->max_logits),
                                  static_cast<const float *>(p->exp_sums), p->context_lens, p->seq_indices,
-                                 p->num_heads, p->max_num_partitions, psize, context_limit(p)));
+                                 p->num_heads, p->max_num_partitions, psize, context_limit(p),
+                                 p->block_table_offsets, log2_pow2(p->block_size)));
   return PA_OK;
 }
 
@@ -394,9 +400,9 @@ bool wants_wide_cta(const pa_params *p) {
   if (get_device_info(&dev) != PA_OK) return false;
   // partitions per sequence: the scratch extent, cut down by the context-length hint if given
   uint32_t parts = p->max_num_partitions;
-  if (p->max_context_len != 0u) {
+  if (context_hint(p) != 0u) {
     const uint32_t psize = (p->head_size == 64u) ? 256u : 512u;
-    parts = std::min(parts, divide_round_up(p->max_context_len, psize));
+    parts = std::min(parts, divide_round_up(context_hint(p), psize));
   }
   const uint64_t items = static_cast<uint64_t>(p->num_kv_heads / 8u) * parts * p->num_seqs;
   return items >= 2ull * static_cast<uint64_t>(dev.sm_count);

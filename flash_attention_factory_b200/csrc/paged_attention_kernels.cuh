@@ -107,6 +107,10 @@ struct AttnArgs {
   // max_blocks_per_seq * block_size (saturated to 32 bits): a context length beyond it is cut
   // to it, so no block-table read leaves the sequence's row whatever context_lens holds
   uint32_t ctx_limit;
+  // optional packed block tables: when set, block_tables is one list of block ids and the row
+  // of sequence i is block_tables[table_offsets[i] .. table_offsets[i + 1]); the limit of a
+  // context then is the length of its own row
+  const uint32_t *table_offsets;
   // optional list of the sequences this launch covers (num_seqs entries); all tensors are
   // still indexed by the sequence ids found in the list
   const uint32_t *seq_indices;
@@ -175,8 +179,22 @@ struct WorkItem {
   uint32_t seq, head_base, partition;
   uint32_t tok_begin, tok_end;
   uint32_t ctx; // context length of the sequence
+  uint32_t table_off; // packed block tables: first entry of the sequence's row
   bool valid;
 };
+
+// Context length of sequence `seq`, cut to what its block-table row can address, and (packed
+// tables) the offset of that row.
+__device__ __forceinline__ uint32_t load_context(const AttnArgs &args, uint32_t seq, uint32_t &table_off) {
+  const uint32_t ctx = __ldg(args.context_lens + seq);
+  if (args.table_offsets == nullptr) {
+    table_off = 0u;
+    return min(ctx, args.ctx_limit);
+  }
+  table_off = __ldg(args.table_offsets + seq);
+  const uint64_t row_tokens = static_cast<uint64_t>(__ldg(args.table_offsets + seq + 1) - table_off) << args.block_shift;
+  return static_cast<uint32_t>(min(static_cast<uint64_t>(ctx), row_tokens));
+}
 
 // Split mode: the work items are the (sequence, partition, head group) triples whose partition
 // starts inside the context, numbered densely with the head group fastest (CTAs that run
@@ -195,13 +213,15 @@ struct SplitCursor {
   uint32_t items_before;   // items of all sequences before the window
   uint32_t lane_seq;       // id of the (window_seq + lane)-th sequence of the launch
   uint32_t lane_ctx;       // its context length (0 past the end of the launch)
+  uint32_t lane_off;       // packed block tables: offset of its row
   uint32_t lane_incl;      // items of sequences window_seq .. window_seq + lane (inclusive scan)
   uint32_t window_items;   // items of the whole window
 
   __device__ __forceinline__ void load_window(const AttnArgs &args, uint32_t groups, uint32_t lane) {
     const uint32_t pos = window_seq + lane;
     lane_seq = (pos < args.num_seqs) ? (args.seq_indices != nullptr ? __ldg(args.seq_indices + pos) : pos) : 0u;
-    lane_ctx = (pos < args.num_seqs) ? min(__ldg(args.context_lens + lane_seq), args.ctx_limit) : 0u;
+    lane_off = 0u;
+    lane_ctx = (pos < args.num_seqs) ? load_context(args, lane_seq, lane_off) : 0u;
     const uint32_t parts = min(divide_round_up(lane_ctx, PARTITION), args.max_num_partitions);
     uint32_t v = parts * groups;
 #pragma unroll
@@ -245,6 +265,7 @@ struct SplitCursor {
     it.tok_begin = it.partition * PARTITION;
     it.tok_end = min(ctx, it.tok_begin + PARTITION);
     it.ctx = ctx;
+    it.table_off = __shfl_sync(0xffffffffu, lane_off, owner);
     it.valid = true;
     return it;
   }
@@ -396,7 +417,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     first.seq = (args.seq_indices != nullptr) ? __ldg(args.seq_indices + position) : position;
     first.head_base = blockIdx.y * hpc;
     first.partition = 0;
-    const uint32_t ctx = min(args.context_lens[first.seq], args.ctx_limit);
+    const uint32_t ctx = load_context(args, first.seq, first.table_off);
     // the context is cut into whole stages, spread evenly over the CTAs of the cluster
     const uint32_t total_stages = divide_round_up(ctx, tps);
     const uint32_t stages_per_rank = divide_round_up(total_stages, num_ranks);
@@ -429,8 +450,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     auto fetch_block_id = [&](const WorkItem &it, uint32_t chunk) -> uint32_t {
       const uint32_t tok = it.tok_begin + chunk * rows;
       if (!it.valid || tok >= it.tok_end) return 0u;
-      return __ldg(args.block_tables + static_cast<size_t>(it.seq) * args.max_blocks_per_seq +
-                   (tok >> args.block_shift));
+      const size_t row = (args.table_offsets != nullptr) ? static_cast<size_t>(it.table_off)
+                                                         : static_cast<size_t>(it.seq) * args.max_blocks_per_seq;
+      return __ldg(args.block_tables + row + (tok >> args.block_shift));
     };
 
     WorkItem cur = first;
@@ -1118,6 +1140,16 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   }
 }
 
+// Context length as the attention kernel cut it (load_context): the merge reads exactly the
+// partitions that kernel wrote.
+__device__ __forceinline__ uint32_t merge_context(const uint32_t *context_lens, uint32_t seq, uint32_t ctx_limit,
+                                                  const uint32_t *table_offsets, uint32_t block_shift) {
+  const uint32_t ctx = context_lens[seq];
+  if (table_offsets == nullptr) return min(ctx, ctx_limit);
+  const uint64_t row_tokens = static_cast<uint64_t>(table_offsets[seq + 1] - table_offsets[seq]) << block_shift;
+  return static_cast<uint32_t>(min(static_cast<uint64_t>(ctx), row_tokens));
+}
+
 // Second kernel of the split-context variant: one CTA per (sequence, head).
 //   M = max_p m_p ; w_p = l_p * exp(m_p - M) ; W = sum w_p
 //   out[d] = sum_p (w_p / W) * tmp_out[p, d]
@@ -1131,7 +1163,7 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
                         const float *__restrict__ max_logits, const float *__restrict__ exp_sums,
                         const uint32_t *__restrict__ context_lens, const uint32_t *__restrict__ seq_indices,
                         uint32_t num_heads, uint32_t max_num_partitions, uint32_t partition_size,
-                        uint32_t ctx_limit) {
+                        uint32_t ctx_limit, const uint32_t *__restrict__ table_offsets, uint32_t block_shift) {
   constexpr uint32_t LANES_PER_ROW = D / 4;         // each lane owns 4 dims (8 bytes)
   constexpr uint32_t ROWS = 128 / LANES_PER_ROW;    // partitions handled in parallel
   constexpr uint32_t UNROLL = 4;                    // rows in flight per thread
@@ -1143,7 +1175,7 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
   // kernel drains; nothing is read before that kernel has completed and its writes are visible.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const uint32_t ctx = min(context_lens[seq], ctx_limit); // cut like the attention kernel cuts it
+  const uint32_t ctx = merge_context(context_lens, seq, ctx_limit, table_offsets, block_shift);
   const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
   const size_t base = (static_cast<size_t>(seq) * num_heads + head) * max_num_partitions;
   __half *orow = out + (static_cast<size_t>(seq) * num_heads + head) * D;
@@ -1241,7 +1273,8 @@ merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict_
                              const uint32_t *__restrict__ context_lens,
                              const uint32_t *__restrict__ seq_indices, uint32_t num_heads,
                              uint32_t num_pairs, uint32_t max_num_partitions, uint32_t partition_size,
-                             uint32_t ctx_limit) {
+                             uint32_t ctx_limit, const uint32_t *__restrict__ table_offsets,
+                             uint32_t block_shift) {
   constexpr uint32_t DPL = D / 32;          // dims per lane: 4 or 2
   constexpr uint32_t ROWS = 128 / (D / 4);  // residue classes of the CTA-per-pair kernel
   const uint32_t lane = threadIdx.x & 31u;
@@ -1252,7 +1285,7 @@ merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict_
   const uint32_t pos = work / num_heads;
   const uint32_t seq = (seq_indices != nullptr) ? __ldg(seq_indices + pos) : pos;
   const uint32_t pair = seq * num_heads + (work - pos * num_heads); // seq * num_heads + head
-  const uint32_t ctx = min(context_lens[seq], ctx_limit);
+  const uint32_t ctx = merge_context(context_lens, seq, ctx_limit, table_offsets, block_shift);
   const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
   const size_t base = static_cast<size_t>(pair) * max_num_partitions;
   const __half *rows = tmp_out + base * D + lane * DPL;

@@ -106,3 +106,117 @@ class BoundStep:
         if rc != _cabi.PA_OK:
             _cabi.check(rc)
         return self.io.out_host
+
+
+def pack_block_tables(block_tables: torch.Tensor, context_lens, block_size: int):
+    """Dense [S, MB] tables -> (ids, offsets): the entries in use, row after row, and the
+    S + 1 row offsets (`pa_params.block_table_offsets`).  Host-side helper."""
+    lens = [int(c) for c in (context_lens.tolist() if torch.is_tensor(context_lens) else context_lens)]
+    counts = [(c + block_size - 1) // block_size for c in lens]
+    offsets = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    offsets[1:] = torch.tensor(counts, dtype=torch.int64).cumsum(0).to(torch.int32)
+    ids = torch.cat([block_tables[i, :n] for i, n in enumerate(counts)]) if lens else block_tables.new_zeros(0)
+    return ids.to(torch.int32).contiguous(), offsets
+
+
+class DecodeBatchIO:
+    """Host and device buffers of a pipelined decode step (`pa_decode_step_host_batch`).
+
+    Pinned host tensors the caller fills (`query_host`, `context_lens_host`, and either the dense
+    `block_tables_host` [S, MB] or, with `packed_capacity`, the packed `block_ids_host` /
+    `block_offsets_host` pair), their device mirrors, and the pinned `out_host`.  `bind()` fixes
+    the entry point and argument block; `BoundBatchStep.run()` is one step: the library cuts the
+    batch into sub-batches and overlaps uploads, kernels and downloads."""
+
+    def __init__(self, num_seqs: int, num_heads: int, head_size: int, max_blocks_per_seq: int, device,
+                 packed_capacity: int = 0):
+        self.device = torch.device(device)
+        s = num_seqs
+        self.packed = packed_capacity > 0
+        self.query_host = torch.empty(s, num_heads, head_size, dtype=torch.float16).pin_memory()
+        self.context_lens_host = torch.zeros(s, dtype=torch.int32).pin_memory()
+        self.out_host = torch.empty(s, num_heads, head_size, dtype=torch.float16).pin_memory()
+        self.query = torch.empty(s, num_heads, head_size, dtype=torch.float16, device=self.device)
+        self.context_lens = torch.zeros(s, dtype=torch.int32, device=self.device)
+        self.out = torch.zeros(s, num_heads, head_size, dtype=torch.float16, device=self.device)
+        if self.packed:
+            self.block_ids_host = torch.zeros(packed_capacity, dtype=torch.int32).pin_memory()
+            self.block_offsets_host = torch.zeros(s + 1, dtype=torch.int32).pin_memory()
+            self.block_ids = torch.zeros(packed_capacity, dtype=torch.int32, device=self.device)
+            self.block_offsets = torch.zeros(s + 1, dtype=torch.int32, device=self.device)
+            # what the entry points take as `block_tables`: a [1, capacity] view of the id list
+            self.block_tables = self.block_ids.view(1, -1)
+        else:
+            self.block_tables_host = torch.zeros(s, max_blocks_per_seq, dtype=torch.int32).pin_memory()
+            self.block_tables = torch.zeros(s, max_blocks_per_seq, dtype=torch.int32, device=self.device)
+
+    def set_block_tables(self, block_tables: torch.Tensor, context_lens, block_size: int) -> None:
+        """Fills the host-side tables from a dense [S, MB] tensor (packing them if this object is packed)."""
+        if not self.packed:
+            self.block_tables_host.copy_(block_tables)
+            return
+        ids, offsets = pack_block_tables(block_tables, context_lens, block_size)
+        if ids.numel() > self.block_ids_host.numel():
+            raise RuntimeError("packed block tables exceed the capacity this DecodeBatchIO was built with")
+        self.block_ids_host[:ids.numel()].copy_(ids)
+        self.block_offsets_host.copy_(offsets)
+
+    @property
+    def h2d_bytes(self) -> int:
+        """Bytes one step uploads with the host buffers as they are filled now."""
+        s = self.query_host.size(0)
+        if self.packed:
+            tables = 4 * (int(self.block_offsets_host[s]) + s + 1)
+        else:
+            tables = self.block_tables_host.numel() * 4
+        return self.query_host.numel() * 2 + 4 * s + tables
+
+    @property
+    def d2h_bytes(self) -> int:
+        return self.out_host.numel() * 2
+
+    def bind(self, entry: str, params: "_cabi.PaParams", sub_batches: int = 0,
+             last_out_direct: bool = True) -> "BoundBatchStep":
+        """`params` is the argument block for this object's device tensors (`query`,
+        `block_tables`, `context_lens`, `out`); with packed tables its `block_table_offsets` is
+        set here."""
+        return BoundBatchStep(self, entry, params, sub_batches, last_out_direct)
+
+
+class BoundBatchStep:
+    """One pipelined decode step on fixed tensors as a single library call."""
+
+    def __init__(self, io: DecodeBatchIO, entry: str, params: "_cabi.PaParams", sub_batches: int,
+                 last_out_direct: bool):
+        self.io = io
+        self.entry = _cabi.ENTRY_IDS[entry]
+        self.params = _cabi.PaParams()
+        ctypes.memmove(ctypes.byref(self.params), ctypes.byref(params), ctypes.sizeof(_cabi.PaParams))
+        self.batch = _cabi.PaHostBatch()
+        self.batch.host_query = io.query_host.data_ptr()
+        self.batch.host_context_lens = io.context_lens_host.data_ptr()
+        self.batch.host_out = io.out_host.data_ptr()
+        if io.packed:
+            self.params.block_tables = io.block_ids.data_ptr()
+            self.params.block_table_offsets = io.block_offsets.data_ptr()
+            self.batch.host_block_tables = io.block_ids_host.data_ptr()
+            self.batch.host_block_table_offsets = io.block_offsets_host.data_ptr()
+        else:
+            self.batch.host_block_tables = io.block_tables_host.data_ptr()
+        self.batch.sub_batches = sub_batches
+        self.batch.flags = _cabi.STEP_LAST_OUT_DIRECT if last_out_direct else 0
+        self._fn = _cabi.load_library().pa_decode_step_host_batch
+        self._device_index = io.device.index if io.device.index is not None else torch.cuda.current_device()
+
+    def run(self, synchronize: bool = True) -> torch.Tensor:
+        """Uploads, launches and downloads on the current stream (and the library's two copy
+        streams); returns the host result, complete if `synchronize`."""
+        if torch.cuda.current_device() != self._device_index:
+            with torch.cuda.device(self.io.device):
+                return self.run(synchronize)
+        stream = torch.cuda.current_stream(self.io.device).cuda_stream
+        rc = self._fn(self.entry, ctypes.byref(self.params), ctypes.byref(self.batch),
+                      ctypes.c_void_p(stream), 1 if synchronize else 0)
+        if rc != _cabi.PA_OK:
+            _cabi.check(rc)
+        return self.io.out_host

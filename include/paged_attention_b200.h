@@ -112,6 +112,15 @@ typedef struct pa_params {
    * calls with disjoint lists can share all buffers, e.g. a loop launch for the short and a
    * reduce launch for the long sequences of one batch.  NULL = sequences 0 .. num_seqs-1. */
   const uint32_t *seq_indices;
+  /* Optional packed block tables (no reference counterpart; the reference's table is the dense
+   * [num_seqs, max_blocks_per_seq] tensor, paged_attention_loop/paged_attention_loop.cpp:57).
+   * A device array of num_seqs + 1 offsets (indexed by sequence id like every other tensor):
+   * block_tables then is one list of block ids and the row of sequence i is
+   * block_tables[block_table_offsets[i] .. block_table_offsets[i + 1]); max_blocks_per_seq is
+   * not used.  A ragged batch's tables shrink from num_seqs * max_blocks_per_seq entries to
+   * the sum of ceil(ctx / block_size), which is what a host uploads per step.  A context
+   * length beyond what its row holds is cut to it.  NULL = dense tables. */
+  const uint32_t *block_table_offsets;
 } pa_params;
 
 /* Tiling knobs of include/paged_attention_policy_v2.hpp for one
@@ -221,6 +230,45 @@ typedef enum pa_entry {
  * pa_params.out) holds the result.  Allocates nothing. */
 PA_API int pa_decode_step_host(int32_t entry, const pa_params *p, const pa_host_step *io, void *stream,
                                int32_t synchronize);
+
+/* Cuts num_seqs sequences into `parts` ranges of consecutive sequences with equal shares of the
+ * KV tokens (host arithmetic, no reference counterpart): range r is [bounds[r], bounds[r + 1])
+ * and ends behind the sequence whose cumulative context length reaches (r + 1) / parts of the
+ * total; ranges may be empty.  Used for the sub-batches of pa_decode_step_host_batch and for
+ * sharding a batch over GPUs by sequence.  `bounds` holds parts + 1 entries. */
+PA_API int pa_split_by_kv_length(const uint32_t *context_lens, uint32_t num_seqs, uint32_t parts, uint32_t *bounds);
+
+/* Host buffers of one decode step for pa_decode_step_host_batch: the caller's per-step inputs
+ * and the result, each in pinned host memory, laid out like their device mirrors in pa_params. */
+typedef struct pa_host_batch {
+  const void *host_query;                   /* fp16 [num_seqs, num_heads, head_size] */
+  const uint32_t *host_block_tables;        /* dense [num_seqs, max_blocks_per_seq], or the packed id list */
+  const uint32_t *host_block_table_offsets; /* [num_seqs + 1] for packed tables, NULL for dense ones */
+  const uint32_t *host_context_lens;        /* [num_seqs] */
+  void *host_out;                           /* fp16 [num_seqs, num_heads, head_size] */
+  uint32_t sub_batches;                     /* 0 = chosen from the step's size; 1 = no overlap; at most 8 */
+  uint32_t flags;                           /* PA_STEP_* */
+} pa_host_batch;
+
+/* The kernels of the last sub-batch write their result straight into host_out (which then has
+ * to be device-accessible pinned memory) instead of a download by the copy engine. */
+#define PA_STEP_LAST_OUT_DIRECT 1u
+
+/* One decode step with host buffers, pipelined (no counterpart in the reference).  The batch is
+ * cut into sub-batches of consecutive sequences holding equal shares of the KV tokens; the
+ * upload of sub-batch k+1 (its rows of query, context lengths and block tables -- only the
+ * entries in use when the tables are packed, see pa_params.block_table_offsets), the kernels of
+ * sub-batch k and the download of sub-batch k-1 run at the same time, on two copy streams the
+ * library creates once per device and on `stream`.  p holds the device mirrors (query,
+ * block_tables, block_table_offsets, context_lens, out, and the scratch of the reduce entry
+ * points), all caller-owned; p->seq_indices must be NULL.  A sub-batch is the same call with
+ * every per-sequence pointer moved to its first row, so results are those of the chosen entry
+ * point on the whole batch for the reduce entry points (bit for bit) and for the loop entry
+ * points whenever the same cluster size is chosen.  With `synchronize` non-zero the call returns
+ * when host_out holds the whole result; otherwise everything is ordered on `stream`.
+ * Allocates no device memory.  One such call at a time per device. */
+PA_API int pa_decode_step_host_batch(int32_t entry, const pa_params *p, const pa_host_batch *io, void *stream,
+                                     int32_t synchronize);
 
 /* Arguments of pa_reshape_and_cache. */
 typedef struct pa_cache_write_params {

@@ -99,3 +99,23 @@ def test_lpt_sharding_is_a_balanced_partition():
         assert max(loads) <= 1.001 * sum(lens) / world
     assert shard_sequences_lpt([], 3) == [[], [], []]
     assert shard_sequences_lpt([5, 5, 5], 2) == [[0, 2], [1]]  # ties: lower id first, lower rank first
+
+
+def test_library_split_agrees_with_the_python_sharding_helper():
+    """pa_split_by_kv_length (the sub-batches of the pipelined host step, the sequence shards of the
+    multi-GPU driver) and sharding.shard_sequences_by_kv_length are the same function."""
+    import random
+
+    from flash_attention_factory_b200 import _cabi, build
+    from flash_attention_factory_b200.sharding import shard_sequences_by_kv_length
+
+    build.build()
+    rng = random.Random(4)
+    cases = [[], [0, 0, 0], [5], [1] * 7, [100, 1, 1, 1, 100], [0, 7, 0, 0, 9, 0]]
+    cases += [[rng.randint(0, 40000) for _ in range(rng.randint(1, 300))] for _ in range(30)]
+    for lens in cases:
+        for parts in (1, 2, 3, 4, 8):
+            got = _cabi.split_by_kv_length(lens, parts)
+            assert got == shard_sequences_by_kv_length(lens, parts), (lens[:10], parts)
+            assert got[0][0] == 0 and got[-1][1] == len(lens)
+            assert all(a[1] == b[0] for a, b in zip(got, got[1:]))
