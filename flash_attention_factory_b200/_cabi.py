@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
     "pa_decode_step_host",
     "pa_decode_step_host_batch",
     "pa_split_by_kv_length",
+    "pa_host_batch_plan",
     "pa_version",
 )
 
@@ -140,6 +141,9 @@ class PaHostBatch(ctypes.Structure):
         ("host_out", ctypes.c_void_p),
         ("sub_batches", ctypes.c_uint32),
         ("flags", ctypes.c_uint32),
+        ("host_staging", ctypes.c_void_p),
+        ("dev_staging", ctypes.c_void_p),
+        ("staging_bytes", ctypes.c_uint64),
     ]
 
 
@@ -190,6 +194,10 @@ def load_library() -> ctypes.CDLL:
     lib.pa_decode_step_host_batch.argtypes = [ctypes.c_int32, ctypes.POINTER(PaParams), ctypes.POINTER(PaHostBatch),
                                               ctypes.c_void_p, ctypes.c_int32]
     lib.pa_decode_step_host_batch.restype = ctypes.c_int
+    lib.pa_host_batch_plan.argtypes = [ctypes.POINTER(PaParams), ctypes.POINTER(PaHostBatch),
+                                       ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint64),
+                                       ctypes.POINTER(ctypes.c_uint64)]
+    lib.pa_host_batch_plan.restype = ctypes.c_int
     lib.pa_split_by_kv_length.argtypes = [ctypes.POINTER(ctypes.c_uint32), ctypes.c_uint32, ctypes.c_uint32,
                                           ctypes.POINTER(ctypes.c_uint32)]
     lib.pa_split_by_kv_length.restype = ctypes.c_int

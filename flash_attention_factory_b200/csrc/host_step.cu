@@ -3,6 +3,7 @@
 //   pa_decode_step_host        one upload, the launch, one download, in order on one stream
 //   pa_decode_step_host_batch  the same step cut into sub-batches of consecutive sequences whose
 //                              uploads, kernels and downloads overlap on three streams
+#include <cmath>
 #include <mutex>
 
 #include "launch_common.cuh"
@@ -59,6 +60,61 @@ T *advance(T *base, size_t bytes) {
                          : reinterpret_cast<T *>(reinterpret_cast<uintptr_t>(base) + bytes);
 }
 
+size_t table_entries_of(const pa_params *p, const pa_host_batch *io) {
+  const uint32_t S = p->num_seqs;
+  return io->host_block_table_offsets != nullptr
+             ? static_cast<size_t>(io->host_block_table_offsets[S] - io->host_block_table_offsets[0])
+             : static_cast<size_t>(S) * p->max_blocks_per_seq;
+}
+
+// Number of sub-batches of a pipelined step.  A further sub-batch costs about 40 us (the ramp
+// and tail of one more launch pair, more copies and events); cutting into n hides (1 - 1/n) of
+// the transfer time, about 16 us of latencies plus the bytes at the 25 GB/s per direction
+// measured for pinned memory on B200 hosts.  The sum is smallest near
+// n = sqrt(transfer time / 40 us).
+uint32_t choose_sub_batches(const pa_params *p, const pa_host_batch *io) {
+  const uint32_t S = p->num_seqs;
+  uint32_t n = io->sub_batches;
+  if (n == 0) {
+    const double row_bytes = 2.0 * p->num_heads * p->head_size;
+    const double bytes = 2.0 * row_bytes * S + 4.0 * (static_cast<double>(table_entries_of(p, io)) + 2.0 * S);
+    const double transfer_us = 16.0 + bytes / 25.0e3;
+    n = static_cast<uint32_t>(std::sqrt(transfer_us / 40.0) + 0.5);
+  }
+  return std::max(1u, std::min(std::min(n, kMaxSubBatches), std::max(S, 1u)));
+}
+
+// The step without sub-batches: uploads, launch and download in order on the caller's stream,
+// no second stream and no events.  When the caller's host inputs are one staging block mirrored
+// on the device (pa_host_batch.host_staging) the upload is a single copy.
+int single_batch_step(int32_t entry, const pa_params *p, const pa_host_batch *io, bool packed, size_t row_bytes,
+                      size_t table_entries, void *stream, int32_t synchronize) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint32_t S = p->num_seqs;
+  if (io->host_staging != nullptr && io->dev_staging != nullptr && io->staging_bytes != 0) {
+    PA_CUDA_TRY(cudaMemcpyAsync(io->dev_staging, io->host_staging, io->staging_bytes, cudaMemcpyHostToDevice, st));
+  } else {
+    PA_CUDA_TRY(cudaMemcpyAsync(const_cast<void *>(p->query), io->host_query, S * row_bytes, cudaMemcpyHostToDevice, st));
+    PA_CUDA_TRY(cudaMemcpyAsync(const_cast<uint32_t *>(p->context_lens), io->host_context_lens, S * sizeof(uint32_t),
+                                cudaMemcpyHostToDevice, st));
+    if (packed)
+      PA_CUDA_TRY(cudaMemcpyAsync(const_cast<uint32_t *>(p->block_table_offsets), io->host_block_table_offsets,
+                                  (S + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
+    if (table_entries != 0) {
+      const size_t first = packed ? io->host_block_table_offsets[0] : 0;
+      PA_CUDA_TRY(cudaMemcpyAsync(const_cast<uint32_t *>(p->block_tables) + first, io->host_block_tables + first,
+                                  table_entries * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
+    }
+  }
+  const bool direct = (io->flags & PA_STEP_LAST_OUT_DIRECT) != 0u;
+  pa_params whole = *p;
+  if (direct) whole.out = io->host_out;
+  if (int rc = launch_entry(entry, &whole, stream)) return rc;
+  if (!direct) PA_CUDA_TRY(cudaMemcpyAsync(io->host_out, p->out, S * row_bytes, cudaMemcpyDeviceToHost, st));
+  if (synchronize != 0) PA_CUDA_TRY(cudaStreamSynchronize(st));
+  return PA_OK;
+}
+
 } // namespace
 } // namespace pa
 
@@ -98,6 +154,24 @@ PA_API int pa_decode_step_host(int32_t entry, const pa_params *p, const pa_host_
   return PA_OK;
 }
 
+PA_API int pa_host_batch_plan(const pa_params *p, const pa_host_batch *io, uint32_t *sub_batches,
+                              uint64_t *h2d_bytes, uint64_t *d2h_bytes) {
+  using namespace pa;
+  if (p == nullptr || io == nullptr || io->host_context_lens == nullptr)
+    return fail(PA_ERR_BAD_ARG, "params, host batch or its context lengths are null");
+  const uint32_t S = p->num_seqs;
+  const uint32_t n = choose_sub_batches(p, io);
+  const uint64_t row_bytes = static_cast<uint64_t>(p->num_heads) * p->head_size * 2;
+  uint64_t up = S * row_bytes + 4ull * S + 4ull * table_entries_of(p, io) +
+                (io->host_block_table_offsets != nullptr ? 4ull * (S + 1) : 0ull);
+  if (n == 1 && io->host_staging != nullptr && io->dev_staging != nullptr && io->staging_bytes != 0)
+    up = io->staging_bytes;
+  if (sub_batches) *sub_batches = n;
+  if (h2d_bytes) *h2d_bytes = up;
+  if (d2h_bytes) *d2h_bytes = S * row_bytes; // by the copy engine or, for a direct last sub-batch, by the kernels
+  return PA_OK;
+}
+
 PA_API int pa_decode_step_host_batch(int32_t entry, const pa_params *p, const pa_host_batch *io, void *stream,
                                      int32_t synchronize) {
   using namespace pa;
@@ -116,15 +190,9 @@ PA_API int pa_decode_step_host_batch(int32_t entry, const pa_params *p, const pa
   if (io->sub_batches > kMaxSubBatches) return fail(PA_ERR_BAD_ARG, "host batch: at most %u sub-batches", kMaxSubBatches);
   const bool reduce = entry == PA_ENTRY_REDUCE || entry == PA_ENTRY_FP8_REDUCE;
   const size_t row_bytes = static_cast<size_t>(p->num_heads) * p->head_size * 2; // one sequence of query / out
-  const size_t table_entries = packed ? io->host_block_table_offsets[S] - io->host_block_table_offsets[0]
-                                      : static_cast<size_t>(S) * p->max_blocks_per_seq;
-  // ---- how many sub-batches: enough bytes to be worth overlapping, enough sequences to cut
-  uint32_t n = io->sub_batches;
-  if (n == 0) {
-    const size_t bytes = 2 * row_bytes * S + 4 * (table_entries + 2 * static_cast<size_t>(S));
-    n = bytes < (256u << 10) ? 1u : (bytes < (2u << 20) ? 2u : 4u);
-  }
-  n = std::min(n, S);
+  const size_t table_entries = table_entries_of(p, io);
+  const uint32_t n = choose_sub_batches(p, io);
+  if (n == 1) return single_batch_step(entry, p, io, packed, row_bytes, table_entries, stream, synchronize);
   // ---- boundaries: equal shares of the batch's KV tokens (the kernels' time follows the tokens)
   uint32_t bound[kMaxSubBatches + 1];
   if (int rc = pa_split_by_kv_length(io->host_context_lens, S, n, bound)) return rc;

@@ -133,22 +133,36 @@ class DecodeBatchIO:
         self.device = torch.device(device)
         s = num_seqs
         self.packed = packed_capacity > 0
-        self.query_host = torch.empty(s, num_heads, head_size, dtype=torch.float16).pin_memory()
-        self.context_lens_host = torch.zeros(s, dtype=torch.int32).pin_memory()
-        self.out_host = torch.empty(s, num_heads, head_size, dtype=torch.float16).pin_memory()
-        self.query = torch.empty(s, num_heads, head_size, dtype=torch.float16, device=self.device)
-        self.context_lens = torch.zeros(s, dtype=torch.int32, device=self.device)
-        self.out = torch.zeros(s, num_heads, head_size, dtype=torch.float16, device=self.device)
+        # one pinned staging block and its device mirror with the same layout:
+        # [query | context_lens | offsets (packed) | block ids or dense tables]
+        q_bytes = s * num_heads * head_size * 2
+        off_cl = _round_up(q_bytes, 256)
+        off_offsets = off_cl + _round_up(4 * s, 256)
+        off_tables = off_offsets + (_round_up(4 * (s + 1), 256) if self.packed else 0)
+        table_entries = packed_capacity if self.packed else s * max_blocks_per_seq
+        total = off_tables + _round_up(4 * table_entries, 256)
+        self.host = torch.zeros(total, dtype=torch.uint8).pin_memory()
+        self.dev = torch.zeros(total, dtype=torch.uint8, device=self.device)
+
+        def views(buf):
+            q = buf[:q_bytes].view(torch.float16).view(s, num_heads, head_size)
+            cl = buf[off_cl:off_cl + 4 * s].view(torch.int32)
+            offsets = buf[off_offsets:off_offsets + 4 * (s + 1)].view(torch.int32) if self.packed else None
+            tables = buf[off_tables:off_tables + 4 * table_entries].view(torch.int32)
+            return q, cl, offsets, tables
+
+        self.query_host, self.context_lens_host, offsets_host, tables_host = views(self.host)
+        self.query, self.context_lens, offsets_dev, tables_dev = views(self.dev)
         if self.packed:
-            self.block_ids_host = torch.zeros(packed_capacity, dtype=torch.int32).pin_memory()
-            self.block_offsets_host = torch.zeros(s + 1, dtype=torch.int32).pin_memory()
-            self.block_ids = torch.zeros(packed_capacity, dtype=torch.int32, device=self.device)
-            self.block_offsets = torch.zeros(s + 1, dtype=torch.int32, device=self.device)
+            self.block_ids_host, self.block_offsets_host = tables_host, offsets_host
+            self.block_ids, self.block_offsets = tables_dev, offsets_dev
             # what the entry points take as `block_tables`: a [1, capacity] view of the id list
             self.block_tables = self.block_ids.view(1, -1)
         else:
-            self.block_tables_host = torch.zeros(s, max_blocks_per_seq, dtype=torch.int32).pin_memory()
-            self.block_tables = torch.zeros(s, max_blocks_per_seq, dtype=torch.int32, device=self.device)
+            self.block_tables_host = tables_host.view(s, max_blocks_per_seq)
+            self.block_tables = tables_dev.view(s, max_blocks_per_seq)
+        self.out_host = torch.empty(s, num_heads, head_size, dtype=torch.float16).pin_memory()
+        self.out = torch.zeros(s, num_heads, head_size, dtype=torch.float16, device=self.device)
 
     def set_block_tables(self, block_tables: torch.Tensor, context_lens, block_size: int) -> None:
         """Fills the host-side tables from a dense [S, MB] tensor (packing them if this object is packed)."""
@@ -160,20 +174,6 @@ class DecodeBatchIO:
             raise RuntimeError("packed block tables exceed the capacity this DecodeBatchIO was built with")
         self.block_ids_host[:ids.numel()].copy_(ids)
         self.block_offsets_host.copy_(offsets)
-
-    @property
-    def h2d_bytes(self) -> int:
-        """Bytes one step uploads with the host buffers as they are filled now."""
-        s = self.query_host.size(0)
-        if self.packed:
-            tables = 4 * (int(self.block_offsets_host[s]) + s + 1)
-        else:
-            tables = self.block_tables_host.numel() * 4
-        return self.query_host.numel() * 2 + 4 * s + tables
-
-    @property
-    def d2h_bytes(self) -> int:
-        return self.out_host.numel() * 2
 
     def bind(self, entry: str, params: "_cabi.PaParams", sub_batches: int = 0,
              last_out_direct: bool = True) -> "BoundBatchStep":
@@ -205,8 +205,18 @@ class BoundBatchStep:
             self.batch.host_block_tables = io.block_tables_host.data_ptr()
         self.batch.sub_batches = sub_batches
         self.batch.flags = _cabi.STEP_LAST_OUT_DIRECT if last_out_direct else 0
+        self.batch.host_staging = io.host.data_ptr()
+        self.batch.dev_staging = io.dev.data_ptr()
+        self.batch.staging_bytes = io.host.numel()
         self._fn = _cabi.load_library().pa_decode_step_host_batch
         self._device_index = io.device.index if io.device.index is not None else torch.cuda.current_device()
+
+    def plan(self) -> dict:
+        """Sub-batch count and bytes moved per step with the host buffers as they are filled now."""
+        n, up, down = ctypes.c_uint32(0), ctypes.c_uint64(0), ctypes.c_uint64(0)
+        _cabi.check(_cabi.load_library().pa_host_batch_plan(ctypes.byref(self.params), ctypes.byref(self.batch),
+                                                            ctypes.byref(n), ctypes.byref(up), ctypes.byref(down)))
+        return {"sub_batches": int(n.value), "h2d_bytes": int(up.value), "d2h_bytes": int(down.value)}
 
     def run(self, synchronize: bool = True) -> torch.Tensor:
         """Uploads, launches and downloads on the current stream (and the library's two copy

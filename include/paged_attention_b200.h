@@ -248,6 +248,13 @@ typedef struct pa_host_batch {
   void *host_out;                           /* fp16 [num_seqs, num_heads, head_size] */
   uint32_t sub_batches;                     /* 0 = chosen from the step's size; 1 = no overlap; at most 8 */
   uint32_t flags;                           /* PA_STEP_* */
+  /* Optional: the host inputs above all lie in ONE pinned staging block of staging_bytes at
+   * host_staging, and the device mirrors in pa_params lie at the same offsets inside the device
+   * block at dev_staging.  A step that is not cut into sub-batches then uploads the block with a
+   * single copy instead of one per tensor (a small step is bound by copy latencies, not bytes). */
+  const void *host_staging;
+  void *dev_staging;
+  uint64_t staging_bytes;
 } pa_host_batch;
 
 /* The kernels of the last sub-batch write their result straight into host_out (which then has
@@ -269,6 +276,11 @@ typedef struct pa_host_batch {
  * Allocates no device memory.  One such call at a time per device. */
 PA_API int pa_decode_step_host_batch(int32_t entry, const pa_params *p, const pa_host_batch *io, void *stream,
                                      int32_t synchronize);
+
+/* What pa_decode_step_host_batch would do with these arguments: the number of sub-batches and
+ * the bytes it moves host -> device and device -> host per step (host arithmetic only). */
+PA_API int pa_host_batch_plan(const pa_params *p, const pa_host_batch *io, uint32_t *sub_batches,
+                              uint64_t *h2d_bytes, uint64_t *d2h_bytes);
 
 /* Arguments of pa_reshape_and_cache. */
 typedef struct pa_cache_write_params {

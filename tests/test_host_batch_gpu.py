@@ -97,7 +97,7 @@ def test_packed_block_tables_give_the_bits_of_dense_tables(cuda_device, variant,
     dev = cuda_device
     s, h, hk, d, bs = len(CTX), 8, 4, 128, 16
     c = make_case(seed=321, num_seqs=s, num_heads=h, num_kv_heads=hk, head_size=d, block_size=bs,
-                  context_lens=CTX, kv_dtype=kv, sinks=True)
+                  context_lens=CTX, kv_dtype=kv)
     mod, args, keep = _setup(dev, kv, variant, None, c, 5, h, hk, d, bs)
     q, bt, cl = c["query"].to(dev), c["block_tables"].to(dev), c["context_lens"].to(dev)
     dense = torch.zeros(s, h, d, dtype=torch.float16, device=dev)
@@ -127,7 +127,7 @@ def test_packed_block_tables_give_the_bits_of_dense_tables(cuda_device, variant,
     c3["context_lens"] = c["context_lens"].clone()
     c3["context_lens"][3] = honest3
     want = oracle.paged_attention_ref(c3["query"], c3["key_cache"], c3["value_cache"], c3["block_tables"],
-                                      c3["context_lens"], sm_scale=c["sm_scale"], sinks=c["sinks"])
+                                      c3["context_lens"], sm_scale=c["sm_scale"])
     assert_close(out.cpu(), want, what="packed row limit")
 
 
