@@ -444,6 +444,30 @@ def timed_calls(call, steps: int, warmup: int, min_seconds: float, group: Group)
     return e0.elapsed_time(e1), cps
 
 
+def timed_launches_from_c(w: Workload, steps: int, warmup: int, min_seconds: float, group: Group):
+    """The same protocol as timed_calls with the calls issued from C (`pa_aid_time_launches`): what
+    a C or C++ host of the library sees.  A Python loop adds several microseconds of interpreter
+    time per call, which hides the kernels of small batches.  One argument block per rotated
+    cache copy, built and checked once."""
+    from flash_attention_factory_b200 import _test_aids
+
+    keep = w.variant
+    w.variant = w.entry_variant()
+    entry = w.module().ENTRY
+    blocks = [w.module().params(*w.args(i)) for i in range(w.copies)]
+    w.variant = keep
+    stream = torch.cuda.current_stream(w.device).cuda_stream
+    _test_aids.time_launches(entry, blocks, max(warmup, 3), stream)
+    group.sync()
+    per_call = _test_aids.time_launches(entry, blocks, 8, stream) * 1e-6
+    per_call = group.max(per_call)[0]
+    cps = max(1, math.ceil(min_seconds / max(per_call * steps, 1e-9)))
+    group.sync()
+    us = _test_aids.time_launches(entry, blocks, steps * cps, stream)
+    group.sync()
+    return us * steps * cps / 1e3, cps
+
+
 def e2e_binding(w: Workload):
     """The host-buffer step of the workload: pinned inputs (query, packed block tables, context
     lengths) and a pinned result, one `pa_decode_step_host_batch` call per step.  Returns
@@ -536,7 +560,10 @@ def measure_workload(w: Workload, a, group: Group, min_seconds: float, e2e_secon
         else:
             w.enqueue(i)
 
-    ms_total, cps = timed_calls(call, a.steps, a.warmup, min_seconds, group)
+    if graphs is None and w.entry_variant() is not None:
+        ms_total, cps = timed_launches_from_c(w, a.steps, a.warmup, min_seconds, group)
+    else:
+        ms_total, cps = timed_calls(call, a.steps, a.warmup, min_seconds, group)
     # ---- per-kernel durations (blocking form of the entry point: events around each kernel)
     attn_us, merge_us = [], []
     if w.entry_variant() is not None:
@@ -601,6 +628,53 @@ def variant_row(m: dict, peak: float, world: int = 1) -> dict:
         row["errors"] = {k: (round(v, 6) if isinstance(v, float) else v) for k, v in m["errors"].items()
                          if k != "checked_ctx"}
     return row
+
+
+def timeline_report(w: Workload, calls: int) -> None:
+    """`--timeline`: per-CTA time stamps of the attention kernel of the last of `calls` back-to-back
+    calls, summarised: microseconds from the first CTA's entry to each event, over the CTAs."""
+    import ctypes
+
+    from flash_attention_factory_b200 import _cabi
+
+    lib = _cabi.load_library()
+    variant = w.entry_variant() or "reduce"
+    reader = getattr(lib, f"pa_debug_timeline_{'fp8_' if w.fp8 else ''}{variant}")
+    for i in range(max(3, calls)):
+        w.enqueue(i)
+    torch.cuda.synchronize(w.device)
+    rows = 4096
+    buf = (ctypes.c_ulonglong * (rows * 8))()
+    _cabi.check(reader(buf, rows))
+    t = torch.tensor(list(buf), dtype=torch.float64).view(rows, 8)
+    t = t[t[:, 0] > 0]
+    t = t[t[:, 5] >= t[:, 0]]  # rows of the last launch only
+    newest = t[:, 0].max()
+    t = t[t[:, 0] > newest - 5e6]
+    t0 = t[:, 0].min()
+    names = ["entry", "after_wait_for_previous_kernel", "first_copy_issued", "first_stage_complete",
+             "last_stage_consumed", "exit"]
+    print(f"{w.spec['name']} {variant}: {t.size(0)} CTAs, kernel span "
+          f"{(t[:, 5].max() - t0) / 1e3:.1f} us, KV bytes {w.kv_bytes}")
+    print(f"{'event (us after first entry)':34s} {'min':>8s} {'p10':>8s} {'median':>8s} {'p90':>8s} {'max':>8s}")
+    for k, name in enumerate(names):
+        col = t[:, k]
+        col = (col[col > 0] - t0) / 1e3
+        if col.numel() == 0:
+            continue
+        q = torch.quantile(col, torch.tensor([0.0, 0.1, 0.5, 0.9, 1.0], dtype=torch.float64))
+        print(f"{name:34s} " + " ".join(f"{x:8.1f}" for x in q.tolist()))
+    end = (t[:, 5] - t0) / 1e3
+    last = (t[:, 4] - t0) / 1e3
+    span = float(end.max())
+    for back in (5.0, 10.0, 20.0):
+        idle = int((last < span - back).sum())
+        print(f"CTAs that had consumed their last stage {back:.0f} us before the end: {idle} of {t.size(0)}")
+    items = t[:, 6]
+    for k in sorted(set(int(x) for x in items.tolist())):
+        sel = items == k
+        print(f"CTAs with {k} work items: {int(sel.sum())}, last stage consumed at median "
+              f"{float(last[sel].median()):.1f} us (min {float(last[sel].min()):.1f}, max {float(last[sel].max()):.1f})")
 
 
 # name -> (config, variant, KV type override)
@@ -677,10 +751,16 @@ def main() -> None:
                          "measures the kernel fed from L2, not an HBM figure)")
     ap.add_argument("--block-order", default=None, choices=["random", "sequential"],
                     help="physical placement of a sequence's blocks (default: a random permutation)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="measuring aid: run one call on the -DPA_TIMELINE build of the library "
+                         "(python -m flash_attention_factory_b200.build --timeline) and print when the CTAs of "
+                         "the attention kernel started, got their first data, finished and left")
     ap.add_argument("--num-seqs", type=int, default=None,
                     help="override the number of sequences (small cases for profiler captures)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
+    if a.timeline:
+        os.environ["PA_B200_LIBRARY_VARIANT"] = "timeline"
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -731,6 +811,9 @@ def main() -> None:
     my_spec, ctx, _ = shard_spec_and_ctx(spec, ctx_all, shard, world, rank)
     w = Workload(my_spec, ctx, device, seed=1000 * seed + rank, variant=variant)
 
+    if a.timeline:
+        timeline_report(w, a.steps)
+        return
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()

@@ -154,6 +154,13 @@ ENTRY_IDS = {"launch_kernels_loop": 0, "launch_kernels_reduce": 1, "launch_kerne
 
 
 def library_path() -> Path:
+    """The product library, or (PA_B200_LIBRARY_VARIANT=<name>) a differently compiled build of it
+    from this same directory, e.g. the one with per-CTA time stamps."""
+    import os
+
+    variant = os.environ.get("PA_B200_LIBRARY_VARIANT", "")
+    if variant and variant.isalnum():
+        return Path(__file__).resolve().parent / f"libpaged_attention_b200_{variant}.so"
     return Path(__file__).resolve().parent / _LIB_NAME
 
 

@@ -14,7 +14,8 @@ from . import _cabi
 _LIB_NAME = "libpaged_attention_b200_test_aids.so"
 _lib = None
 
-EXPORTED_SYMBOLS = ("pa_aid_selftest_wait_timeout", "pa_aid_measure_read_bandwidth", "pa_aid_last_error")
+EXPORTED_SYMBOLS = ("pa_aid_selftest_wait_timeout", "pa_aid_measure_read_bandwidth", "pa_aid_time_launches",
+                    "pa_aid_last_error")
 
 
 def library_path() -> Path:
@@ -35,6 +36,9 @@ def load_library() -> ctypes.CDLL:
                                                   ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32,
                                                   ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]
     lib.pa_aid_measure_read_bandwidth.restype = ctypes.c_int
+    lib.pa_aid_time_launches.argtypes = [ctypes.c_void_p, ctypes.POINTER(_cabi.PaParams), ctypes.c_uint32,
+                                         ctypes.c_uint32, ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]
+    lib.pa_aid_time_launches.restype = ctypes.c_int
     lib.pa_aid_last_error.argtypes = []
     lib.pa_aid_last_error.restype = ctypes.c_char_p
     _lib = lib
@@ -62,3 +66,17 @@ def measure_read_bandwidth(ptr: int, nbytes: int, iters: int = 10, stream: int =
                                                         nbytes2, method, iters, ctypes.c_void_p(stream),
                                                         ctypes.byref(rate)))
     return float(rate.value)
+
+
+def time_launches(entry: str, params_list, calls: int, stream: int = 0) -> float:
+    """Mean microseconds per call of `calls` back-to-back asynchronous calls of the product entry
+    point `entry`, issued from C, call i with params_list[i % len(params_list)]."""
+    product = _cabi.load_library()
+    fn = ctypes.cast(getattr(product, entry), ctypes.c_void_p)
+    arr = (_cabi.PaParams * len(params_list))()
+    for i, p in enumerate(params_list):
+        ctypes.memmove(ctypes.byref(arr[i]), ctypes.byref(p), ctypes.sizeof(_cabi.PaParams))
+    us = ctypes.c_float(0.0)
+    _check(load_library().pa_aid_time_launches(fn, arr, len(params_list), calls, ctypes.c_void_p(stream),
+                                               ctypes.byref(us)))
+    return float(us.value)

@@ -63,9 +63,9 @@ def needs_build() -> bool:
     return _newest_mtime(deps) > min(LIB_PATH.stat().st_mtime, AIDS_LIB_PATH.stat().st_mtime)
 
 
-def _compile_one(nvcc: str, src: str, verbose: bool) -> Path:
-    obj = BUILD_DIR / (Path(src).stem + ".o")
-    cmd = [nvcc, *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "-c", str(CSRC / src), "-o", str(obj)]
+def _compile_one(nvcc: str, src: str, verbose: bool, defines=(), build_dir: Path = BUILD_DIR) -> Path:
+    obj = build_dir / (Path(src).stem + ".o")
+    cmd = [nvcc, *NVCC_FLAGS, *defines, f"-I{INCLUDE}", f"-I{CSRC}", "-c", str(CSRC / src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -95,12 +95,33 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+def build_variant(name: str, defines) -> Path:
+    """Builds the product library once more with extra -D flags as
+    libpaged_attention_b200_<name>.so (measuring aids such as -DPA_TIMELINE, tuning builds with
+    -DPA_TUNING_KNOBS); `PA_B200_LIBRARY_VARIANT=<name>` makes the package load it."""
+    nvcc = find_nvcc()
+    bdir = PKG_DIR / f"build_{name}"
+    bdir.mkdir(exist_ok=True)
+    with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        objs = list(pool.map(lambda s: _compile_one(nvcc, s, False, list(defines), bdir), SOURCES))
+    target = PKG_DIR / f"libpaged_attention_b200_{name}.so"
+    res = subprocess.run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(target),
+                          *map(str, objs)], capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    return target
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register / smem usage")
+    ap.add_argument("--timeline", action="store_true",
+                    help="also build libpaged_attention_b200_timeline.so (-DPA_TIMELINE: per-CTA time stamps)")
     a = ap.parse_args()
     print(build(force=a.force, verbose=a.verbose))
+    if a.timeline:
+        print(build_variant("timeline", ["-DPA_TIMELINE"]))
 
 
 if __name__ == "__main__":

@@ -161,16 +161,23 @@ inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_cou
   }();
   if (forced != 0) return static_cast<uint32_t>(forced);
 #endif
+  // Any size up to 8 is portable, not only powers of two.  With fewer units than CTA slots the
+  // cluster is as large as still lets every cluster be resident at once (one wave, no slot
+  // left empty that a whole cluster could fill).  With more units than that the CTAs run in
+  // waves and every further CTA costs a launch ramp and a merge (measured on 1024 ragged
+  // sequences: clusters of 2 are 6 % faster than single CTAs, clusters of 3 already 5 % slower),
+  // so clusters of 2 are used, which halve the time a CTA spends on the longest sequence, unless
+  // the contexts are known to be short.
   const uint64_t units = static_cast<uint64_t>(p->num_seqs) * (p->num_kv_heads / hpc);
-  const uint64_t want = 2ull * static_cast<uint64_t>(sm_count);
-  uint32_t cs = 1;
-  while (cs < 8 && units * cs < want) cs *= 2;
+  const uint64_t slots = 2ull * static_cast<uint64_t>(sm_count);
+  uint32_t cs = units >= slots ? 1u : static_cast<uint32_t>(std::min<uint64_t>(8ull, slots / units));
+  if (cs == 1 && (units < 2 * slots || context_hint(p) == 0 || context_hint(p) >= 2048u)) cs = 2;
   if (context_hint(p) != 0) {
-    // a CTA should own at least 8 stages of the longest context: below that the cluster merge
-    // and the extra launches cost more than the split saves (config 1: 24 us unsplit, 36 us
-    // with 8 CTAs per cluster)
+    // a CTA should own at least kMinStagesPerCta stages of the longest context: below that the
+    // cluster merge and the extra CTAs cost more than the split saves
+    constexpr uint32_t kMinStagesPerCta = 4;
     const uint32_t stages = divide_round_up(context_hint(p), tokens_per_stage);
-    while (cs > 1 && stages / cs < 8) cs /= 2;
+    while (cs > 1 && stages / cs < kMinStagesPerCta) --cs;
   }
   return cs;
 }
@@ -425,6 +432,20 @@ inline int dispatch_merge(const pa_params *p, cudaStream_t stream) {
   if (p->head_size == 128) return enqueue_merge<128>(p, stream);
   return enqueue_merge<64>(p, stream);
 }
+
+// A -DPA_TIMELINE build exports, per launcher, a reader of its unit's time-stamp table
+// (`ctas` rows of 8 values; see g_timeline).  Synchronises the device.
+#ifdef PA_TIMELINE
+#define PA_TIMELINE_ACCESSOR(name)                                                                    \
+  extern "C" PA_API int name(unsigned long long *dst, uint32_t ctas) {                                \
+    if (dst == nullptr || ctas > ::pa::kTimelineCtas) return ::pa::fail(PA_ERR_BAD_ARG, "timeline: bad arguments"); \
+    PA_CUDA_TRY(cudaDeviceSynchronize());                                                             \
+    PA_CUDA_TRY(cudaMemcpyFromSymbol(dst, ::pa::g_timeline, sizeof(unsigned long long) * 8 * ctas));  \
+    return PA_OK;                                                                                     \
+  }
+#else
+#define PA_TIMELINE_ACCESSOR(name)
+#endif
 
 // reads and clears this translation unit's copy of the device status word
 inline int read_and_clear_device_status(int *value) {

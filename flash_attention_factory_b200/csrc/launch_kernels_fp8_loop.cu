@@ -10,6 +10,8 @@ namespace pa {
 int read_status_fp8_loop(int *v) { return read_and_clear_device_status(v); }
 } // namespace pa
 
+PA_TIMELINE_ACCESSOR(pa_debug_timeline_fp8_loop)
+
 extern "C" PA_API int launch_kernels_fp8_loop(const pa_params *p, void *stream, float *us_out) {
   using namespace pa;
   if (int rc = validate_params(p, /*fp8_entry=*/true, /*needs_scratch=*/false)) return rc;

@@ -7,6 +7,8 @@ namespace pa {
 int read_status_loop(int *v) { return read_and_clear_device_status(v); }
 } // namespace pa
 
+PA_TIMELINE_ACCESSOR(pa_debug_timeline_loop)
+
 extern "C" PA_API int launch_kernels_loop(const pa_params *p, void *stream, float *us_out) {
   using namespace pa;
   if (int rc = validate_params(p, /*fp8_entry=*/false, /*needs_scratch=*/false)) return rc;

@@ -10,6 +10,8 @@ namespace pa {
 int read_status_reduce(int *v) { return read_and_clear_device_status(v); }
 } // namespace pa
 
+PA_TIMELINE_ACCESSOR(pa_debug_timeline_reduce)
+
 extern "C" PA_API int launch_kernels_reduce(const pa_params *p, void *stream, float *us_out) {
   using namespace pa;
   if (int rc = validate_params(p, /*fp8_entry=*/false, /*needs_scratch=*/true)) return rc;

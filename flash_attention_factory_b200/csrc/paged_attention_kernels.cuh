@@ -75,6 +75,27 @@ inline uint32_t next_sched_slot(bool capturing) {
   return g_next_direct_slot.fetch_add(1, std::memory_order_relaxed) % kDirectSchedSlots;
 }
 
+// Per-CTA time stamps (%globaltimer, ns), compiled in with -DPA_TIMELINE only: a measuring aid
+// for the launch ramp and the tail of a launch.  One row per CTA of the most recent launch of
+// this translation unit: [0] kernel entry, [1] after the wait for the previous kernel,
+// [2] first copy issued, [3] first stage complete, [4] last stage of the last item consumed,
+// [5] exit, [6] work items done, [7] SM id.
+#ifdef PA_TIMELINE
+constexpr uint32_t kTimelineCtas = 4096;
+static __device__ unsigned long long g_timeline[kTimelineCtas][8];
+#define PA_STAMP(slot)                                                                          \
+  do {                                                                                          \
+    if (timeline_cta < kTimelineCtas) g_timeline[timeline_cta][slot] = global_timer_ns();       \
+  } while (0)
+#define PA_STAMP_VALUE(slot, v)                                                                 \
+  do {                                                                                          \
+    if (timeline_cta < kTimelineCtas) g_timeline[timeline_cta][slot] = (v);                     \
+  } while (0)
+#else
+#define PA_STAMP(slot) do { } while (0)
+#define PA_STAMP_VALUE(slot, v) do { } while (0)
+#endif
+
 struct AttnArgs {
   const __half *query;
   __half *out;
@@ -331,6 +352,19 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t hpc = args.hpc;
   const uint32_t tps = args.tokens_per_stage;
+#ifdef PA_TIMELINE
+  const uint32_t timeline_cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (threadIdx.x == 32) {
+    uint32_t smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    PA_STAMP(0);
+    PA_STAMP_VALUE(2, 0ull);
+    PA_STAMP_VALUE(3, 0ull);
+    PA_STAMP_VALUE(4, 0ull);
+    PA_STAMP_VALUE(6, 0ull);
+    PA_STAMP_VALUE(7, static_cast<unsigned long long>(smid));
+  }
+#endif
 
   // ---- barriers first: none of this touches global memory, so in split mode it runs before
   // the wait for the previous kernel of the stream
@@ -345,6 +379,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
     *abort_flag = 0u;
     mbar_fence_init();
+    // the descriptors are kernel parameters, not data of an earlier kernel: fetch them now
+    tma_prefetch_descriptor(&tmap_k);
+    tma_prefetch_descriptor(&tmap_v);
   }
   __syncthreads();
 
@@ -361,6 +398,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     // this grid may itself have been scheduled while the previous kernel of the stream was
     // draining: nothing in global memory is touched before that kernel has completed
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 32) PA_STAMP(1);
     cursor.init(args, head_groups, lane);
     first = cursor.seek(blockIdx.x, args, head_groups, lane);
   } else {
@@ -374,6 +412,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     // bound by launch latency otherwise)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 32) PA_STAMP(1);
     // Clusters start in block-index order.  With ragged lengths a long sequence that starts
     // last leaves the machine idle behind it, so block index z is mapped to the z-th sequence
     // in (approximately) descending length: 16 length classes, longest class first, position
@@ -429,10 +468,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
 
   if (warp == 0) {
     // =========================== producer warp ===========================
-    if (lane == 0) {
-      tma_prefetch_descriptor(&tmap_k);
-      tma_prefetch_descriptor(&tmap_v);
-    }
     const uint64_t kv_policy = l2_evict_first_policy(); // every KV byte is read once
     const uint32_t rows = args.rows_per_box;
     const uint32_t bps = args.boxes_per_stage;
@@ -461,13 +496,18 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     while (cur.valid && alive) {
       WorkItem nxt{};
       nxt.valid = false;
+      // Dynamic scheduling (split mode): the CTA's first item is its block index, every further
+      // one is drawn from a global counter, so CTAs that run faster take more items.  The
+      // draw is issued here and its answer is only looked at after this item's first copies
+      // have been issued, so the round trip of the atomic never delays a copy.  The number is
+      // published to the consumer warps through a two-entry queue in shared memory.
+      unsigned int ticket = 0;
+      bool next_known = (MODE != MODE_SPLIT);
       if constexpr (MODE == MODE_SPLIT) {
-        // Dynamic scheduling: the CTA's first item is its block index, every further one is
-        // drawn from a global counter, so CTAs that run faster take more items.  The number
-        // is published to the consumer warps through a two-entry queue in shared memory.
-        uint32_t next_index = 0;
-        if (lane == 0) next_index = gridDim.x + atomicAdd(&g_sched[args.sched_slot][0], 1u);
-        next_index = __shfl_sync(0xffffffffu, next_index, 0);
+        if (lane == 0) ticket = atomicAdd(&g_sched[args.sched_slot][0], 1u);
+      }
+      auto resolve_next = [&]() {
+        const uint32_t next_index = gridDim.x + __shfl_sync(0xffffffffu, ticket, 0);
         nxt = cursor.seek(next_index, args, head_groups, lane);
         const uint32_t entry = item_no + 1, qs = entry & 1u, use = (entry - 1u) >> 1; // n-th use of the slot
         if (lane == 0) {
@@ -478,11 +518,17 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           }
         }
         alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
-        if (!alive) break;
-      }
+        next_known = true;
+      };
       const uint32_t total_chunks = divide_round_up(cur.tok_end - cur.tok_begin, rows);
       const int32_t head_coord = static_cast<int32_t>(cur.head_base + lane_head);
+      // The number is needed at the item's last batch, which prefetches the next item's table
+      // entries; the consumers ask for it when they have consumed this item's last stage.
       for (uint32_t chunk0 = 0; chunk0 < total_chunks && alive; chunk0 += chunks_per_batch) {
+        if (!next_known && chunk0 + chunks_per_batch >= total_chunks) {
+          resolve_next();
+          if (!alive) break;
+        }
         const uint32_t chunk = chunk0 + lane_chunk;
         const uint32_t block_id = block_id_next;
         // prefetch the table entries of the next batch (of this item or of the next one)
@@ -509,6 +555,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
             // several heads lands as [head][row][slab], which is this very layout
             const uint32_t row0 = lane_head * tps + (lane_chunk % chunks_per_stage) * rows;
             const uint32_t stage_base = ring_base + slot * L::STAGE_BYTES;
+#ifdef PA_TIMELINE
+            if (lane == 0 && item_no == 0 && chunk0 == 0 && sb == 0) PA_STAMP(2);
+#endif
 #pragma unroll
             for (uint32_t sl = 0; sl < geo::num_slabs; ++sl) {
               const uint32_t dst = stage_base + sl * L::SLAB_TILE + row0 * geo::slab_bytes;
@@ -523,6 +572,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           }
         }
       }
+      if (!next_known && alive) resolve_next();
       cur = nxt;
       ++item_no;
     }
@@ -674,6 +724,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
 
     uint32_t slot = 0, phase = 0, item_parity = 0;
     bool alive = true;
+#ifdef PA_TIMELINE
+    bool timeline_first = true;
+    unsigned long long timeline_items = 0;
+#endif
     uint32_t qf[KSTEPS][2];
     WorkItem cur = first;
     if (cur.valid) load_q_fragments<D, KV>(qf, args, cur.seq, cur.head_base + my_head, gid, t4);
@@ -687,19 +741,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     while (cur.valid) {
       WorkItem nxt{};
       nxt.valid = false;
-      if constexpr (MODE == MODE_SPLIT) {
-        // the producer has published the number of the next item (or "none") before it
-        // started to load this one
-        const uint32_t entry = item_no + 1, qs = entry & 1u, use = (entry - 1u) >> 1; // n-th use of the slot
-        if (*abort_flag != 0u) alive = false;
-        uint32_t next_index = kNoItem;
-        if (alive) alive = mbar_wait_bounded(&sched_full[qs], use & 1u, abort_flag);
-        if (alive) next_index = sched_item[qs];
-        __syncwarp();
-        if (alive && lane == 0) mbar_arrive(&sched_empty[qs]);
-        if (next_index != kNoItem) nxt = cursor.seek(next_index, args, head_groups, lane);
-        ++item_no;
-      }
       const uint32_t kv_head = cur.head_base + my_head;
       // softmax scale (log2 domain) and output scale of this warp's KV head
       const float scale = (args.k_scale_per_head != nullptr)
@@ -751,6 +792,12 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         // after an abort the loops keep their shape (the named barriers below need every
         // consumer warp) but no longer wait or compute
         if (alive) alive = mbar_wait_bounded(&full_bar[slot_a], phase_a, abort_flag);
+#ifdef PA_TIMELINE
+        if (ctid == 0 && timeline_first) {
+          PA_STAMP(3);
+          timeline_first = false;
+        }
+#endif
         if (alive && has_b) alive = mbar_wait_bounded(&full_bar[slot_b], phase_b, abort_flag);
         const uint32_t tok_a = st * tps + my_slice * 16; // first token of this warp's tile A
         const uint32_t tok_b = tok_a + tps;
@@ -903,6 +950,25 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
       }
 
+#ifdef PA_TIMELINE
+      if (ctid == 0) {
+        PA_STAMP(4);
+        PA_STAMP_VALUE(6, ++timeline_items);
+      }
+#endif
+      if constexpr (MODE == MODE_SPLIT) {
+        // the producer publishes the number of the next item (or "none") while it loads this
+        // one, at the latest with the item's last batch of copies
+        const uint32_t entry = item_no + 1, qs = entry & 1u, use = (entry - 1u) >> 1; // n-th use of the slot
+        if (*abort_flag != 0u) alive = false;
+        uint32_t next_index = kNoItem;
+        if (alive) alive = mbar_wait_bounded(&sched_full[qs], use & 1u, abort_flag);
+        if (alive) next_index = sched_item[qs];
+        __syncwarp();
+        if (alive && lane == 0) mbar_arrive(&sched_empty[qs]);
+        if (next_index != kNoItem) nxt = cursor.seek(next_index, args, head_groups, lane);
+        ++item_no;
+      }
       // Q of the next item: issued now so that the loads fly during the epilogue below
       if (nxt.valid) load_q_fragments<D, KV>(qf, args, nxt.seq, nxt.head_base + my_head, gid, t4);
 
@@ -1078,49 +1144,103 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     // cluster barriers, also after an abort.
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();
+    if (num_ranks == 1) __syncthreads(); // a lone CTA has no peer to wait for
+    else cluster.sync();
     if (warp != 0) {
+      // A unit of the merge is one output row (KV head hh of the CTA's group, query column g)
+      // times one chunk of 32 dims.  Unit u belongs to CTA u mod num_ranks and, there, to warp
+      // (u / num_ranks) mod NW.  The sources of a row are the R = num_ranks * slices warps that
+      // hold a part of its tokens; lane j of the merging warp fetches source j's (m, l), so the
+      // row statistics take one round trip through distributed shared memory, and the R partial
+      // rows of a chunk are requested together before the first is used: a warp's units cost
+      // two round trips, not two per source.  All sums run in a fixed order.
       const uint32_t G = args.group;
       const bool ok = (*abort_flag == 0u);
-      const uint32_t ctid = threadIdx.x - 32;
+      const uint32_t cw = warp - 1;
       const uint32_t slices = NW / hpc;
-      // each CTA of the cluster writes the dims d with d mod num_ranks == its rank
-      const uint32_t dims_per_rank = (D - cta_rank + num_ranks - 1) / num_ranks;
+      const uint32_t R = num_ranks * slices; // <= 8 * 4 = 32
+      constexpr uint32_t CHUNKS = D / 32;
+      constexpr uint32_t UB = 4; // units of one pass
+      const uint32_t units = hpc * G * CHUNKS;
       float *areas = reinterpret_cast<float *>(smem);
-      for (uint32_t idx = ctid; idx < hpc * 8 * dims_per_rank; idx += NCONS) {
-        const uint32_t hh = idx / (8 * dims_per_rank);
-        const uint32_t g = (idx / dims_per_rank) % 8;
-        const uint32_t d = cta_rank + (idx % dims_per_rank) * num_ranks;
-        float m_all = neg_infinity();
-        for (uint32_t r = 0; r < num_ranks; ++r) {
-          const float *peer = cluster.map_shared_rank(areas, r);
-          for (uint32_t w = hh * slices; w < (hh + 1) * slices; ++w)
-            m_all = fmaxf(m_all, peer[w * L::WARP_AREA_FLOATS + 8 * D + g]);
+      const float *lane_src = cluster.map_shared_rank(areas, (lane < R) ? lane / slices : 0u) +
+                              (lane % slices) * L::WARP_AREA_FLOATS;
+      for (uint32_t k0 = cw; cta_rank + num_ranks * k0 < units; k0 += NW * UB) {
+        uint32_t row_g[UB], row_hh[UB], chunk[UB];
+        bool valid[UB];
+        float f[UB], l_all[UB];
+#pragma unroll
+        for (uint32_t q = 0; q < UB; ++q) {
+          const uint32_t u = cta_rank + num_ranks * (k0 + q * NW);
+          valid[q] = u < units;
+          const uint32_t row = valid[q] ? u / CHUNKS : 0u;
+          chunk[q] = valid[q] ? u % CHUNKS : 0u;
+          row_hh[q] = row / G;
+          row_g[q] = row - row_hh[q] * G;
         }
-        float l_all = 0.f, o_all = 0.f;
-        for (uint32_t r = 0; r < num_ranks; ++r) {
-          const float *peer = cluster.map_shared_rank(areas, r);
-          for (uint32_t w = hh * slices; w < (hh + 1) * slices; ++w) {
-            const float *pa = peer + w * L::WARP_AREA_FLOATS;
-            const float mr = pa[8 * D + g];
-            const float f = (mr == neg_infinity()) ? 0.f : fast_exp2(mr - m_all);
-            l_all += f * pa[8 * D + 8 + g];
-            o_all += f * pa[g * D + d];
+        float m_src[UB], l_src[UB];
+#pragma unroll
+        for (uint32_t q = 0; q < UB; ++q) {
+          m_src[q] = neg_infinity();
+          l_src[q] = 0.f;
+          if (valid[q] && lane < R) {
+            const float *pa = lane_src + row_hh[q] * slices * L::WARP_AREA_FLOATS + 8 * D;
+            m_src[q] = pa[row_g[q]];
+            l_src[q] = pa[8 + row_g[q]];
           }
         }
-        if (g < G && ok) {
-          // acc * (1 / l) as the reference does (paged_attention_utils.hpp:834-835);
-          // an empty context (l = 0) gives zeros
-          const float inv = (l_all > 0.f) ? (1.f / l_all) : 0.f;
-          const size_t head = static_cast<size_t>(first.seq) * args.num_heads + (first.head_base + hh) * G + g;
-          const float head_scale = (args.v_scale_per_head != nullptr)
-                                       ? __ldg(args.v_scale_per_head + first.head_base + hh)
-                                       : args.out_scale;
-          args.out[head * D + d] = __float2half_rn(o_all * head_scale * inv);
+#pragma unroll
+        for (uint32_t q = 0; q < UB; ++q) {
+          float m_all = m_src[q];
+#pragma unroll
+          for (uint32_t o = 16; o > 0; o >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
+          f[q] = (m_src[q] == neg_infinity()) ? 0.f : fast_exp2(m_src[q] - m_all);
+          float l_sum = f[q] * l_src[q];
+#pragma unroll
+          for (uint32_t o = 16; o > 0; o >>= 1) l_sum += __shfl_xor_sync(0xffffffffu, l_sum, o);
+          l_all[q] = l_sum;
+        }
+        float o_all[UB] = {0.f, 0.f, 0.f, 0.f};
+        for (uint32_t j0 = 0; j0 < R; j0 += 8) {
+          float v[UB][8];
+#pragma unroll
+          for (uint32_t q = 0; q < UB; ++q) {
+#pragma unroll
+            for (uint32_t jj = 0; jj < 8; ++jj) {
+              const uint32_t j = j0 + jj;
+              v[q][jj] = 0.f;
+              if (valid[q] && j < R) {
+                const float *pj = cluster.map_shared_rank(areas, j / slices) +
+                                  (row_hh[q] * slices + j % slices) * L::WARP_AREA_FLOATS;
+                v[q][jj] = pj[row_g[q] * D + chunk[q] * 32 + lane];
+              }
+            }
+          }
+#pragma unroll
+          for (uint32_t q = 0; q < UB; ++q) {
+#pragma unroll
+            for (uint32_t jj = 0; jj < 8; ++jj) {
+              const float fj = __shfl_sync(0xffffffffu, f[q], (j0 + jj) & 31u);
+              if (j0 + jj < R) o_all[q] += fj * v[q][jj];
+            }
+          }
+        }
+#pragma unroll
+        for (uint32_t q = 0; q < UB; ++q) {
+          if (valid[q] && ok) {
+            // acc * (1 / l) as the reference does (paged_attention_utils.hpp:834-835);
+            // an empty context (l = 0) gives zeros
+            const float inv = (l_all[q] > 0.f) ? (1.f / l_all[q]) : 0.f;
+            const uint32_t kv_head = first.head_base + row_hh[q];
+            const size_t head = static_cast<size_t>(first.seq) * args.num_heads + kv_head * G + row_g[q];
+            const float head_scale = (args.v_scale_per_head != nullptr) ? __ldg(args.v_scale_per_head + kv_head)
+                                                                        : args.out_scale;
+            args.out[head * D + chunk[q] * 32 + lane] = __float2half_rn(o_all[q] * head_scale * inv);
+          }
         }
       }
     }
-    cluster.sync(); // peers may still be reading this CTA's shared memory
+    if (num_ranks > 1) cluster.sync(); // peers may still be reading this CTA's shared memory
   }
   if constexpr (MODE == MODE_SPLIT) {
     if (threadIdx.x == 0) {
@@ -1134,6 +1254,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       }
     }
   }
+  if (threadIdx.x == 32) PA_STAMP(5);
   if (*abort_flag != 0u) {
     __nanosleep(200000); // give copies that are still in flight time to land
     if (threadIdx.x == 32) atomicExch(&g_pa_device_status, 4);
@@ -1155,8 +1276,18 @@ __device__ __forceinline__ uint32_t merge_context(const uint32_t *context_lens, 
 //   out[d] = sum_p (w_p / W) * tmp_out[p, d]
 // over the partitions p < ceil(ctx / partition_size) only
 // (reference paged_attention_kernel_v2.hpp:679,736-764,813-863,924-932).
-// Latency-bound: the partial-output rows are requested before the weights are known, four
-// rows per warp in flight, so that a typical call costs little more than one memory round trip.
+// Latency-bound: a thread owns 8 dims (one 16-byte load) of kMergeUnroll partial rows, which
+// are requested together with the statistics, before the weights are known; up to
+// kMergeUnroll * ROWS partitions (64 for head size 128: a context of 32768 tokens) cost one
+// memory round trip after the context length has arrived.
+constexpr uint32_t kMergeUnroll = 8; // partial rows in flight per thread
+
+template <int D>
+struct MergeShape {
+  static constexpr uint32_t LANES_PER_ROW = D / 8;        // each lane owns 8 dims (16 bytes)
+  static constexpr uint32_t ROWS = 128 / LANES_PER_ROW;   // partitions handled in parallel: 8 or 16
+};
+
 template <int D>
 __global__ void __launch_bounds__(128)
 merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp_out,
@@ -1164,9 +1295,9 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
                         const uint32_t *__restrict__ context_lens, const uint32_t *__restrict__ seq_indices,
                         uint32_t num_heads, uint32_t max_num_partitions, uint32_t partition_size,
                         uint32_t ctx_limit, const uint32_t *__restrict__ table_offsets, uint32_t block_shift) {
-  constexpr uint32_t LANES_PER_ROW = D / 4;         // each lane owns 4 dims (8 bytes)
-  constexpr uint32_t ROWS = 128 / LANES_PER_ROW;    // partitions handled in parallel
-  constexpr uint32_t UNROLL = 4;                    // rows in flight per thread
+  constexpr uint32_t LANES_PER_ROW = MergeShape<D>::LANES_PER_ROW;
+  constexpr uint32_t ROWS = MergeShape<D>::ROWS;
+  constexpr uint32_t UNROLL = kMergeUnroll;
   constexpr uint32_t WEIGHT_CACHE = 1024;           // weights kept in shared memory
   const uint32_t head = blockIdx.x;
   const uint32_t seq = (seq_indices != nullptr) ? __ldg(seq_indices + blockIdx.y) : blockIdx.y;
@@ -1185,13 +1316,13 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
   __shared__ float part[ROWS][D];
 
   const uint32_t row = tid / LANES_PER_ROW;
-  const uint32_t col = (tid % LANES_PER_ROW) * 4;
+  const uint32_t col = (tid % LANES_PER_ROW) * 8;
   // first UNROLL rows of this thread: requested now, used after the weights are ready
-  uint2 raw[UNROLL];
+  uint4 raw[UNROLL];
 #pragma unroll
   for (uint32_t u = 0; u < UNROLL; ++u) {
     const uint32_t p = row + u * ROWS;
-    raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint2 *>(tmp_out + (base + p) * D + col)) : make_uint2(0u, 0u);
+    raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint4 *>(tmp_out + (base + p) * D + col)) : make_uint4(0u, 0u, 0u, 0u);
   }
 
   // global max over partitions
@@ -1220,14 +1351,15 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
     return (p < WEIGHT_CACHE) ? weights[p] : exp_sums[base + p] * __expf(max_logits[base + p] - m);
   };
 
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  auto accumulate = [&](uint2 v, float w) {
-    const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
-    const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
-    a0 += w * v01.x;
-    a1 += w * v01.y;
-    a2 += w * v23.x;
-    a3 += w * v23.y;
+  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  auto accumulate = [&](const uint4 &v, float w) {
+    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&words[i]));
+      a[2 * i] += w * f.x;
+      a[2 * i + 1] += w * f.y;
+    }
   };
   // partitions are taken in increasing order per thread: the sum has a fixed order
 #pragma unroll
@@ -1239,7 +1371,7 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
 #pragma unroll
     for (uint32_t u = 0; u < UNROLL; ++u) {
       const uint32_t p = p0 + u * ROWS;
-      raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint2 *>(tmp_out + (base + p) * D + col)) : make_uint2(0u, 0u);
+      raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint4 *>(tmp_out + (base + p) * D + col)) : make_uint4(0u, 0u, 0u, 0u);
     }
 #pragma unroll
     for (uint32_t u = 0; u < UNROLL; ++u) {
@@ -1247,16 +1379,18 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
       if (p < np) accumulate(raw[u], weight_of(p) * inv_w);
     }
   }
-  part[row][col] = a0;
-  part[row][col + 1] = a1;
-  part[row][col + 2] = a2;
-  part[row][col + 3] = a3;
-  __syncthreads();
-  if (tid < D) {
-    float s = 0.f;
 #pragma unroll
-    for (uint32_t r = 0; r < ROWS; ++r) s += part[r][tid];
-    orow[tid] = __float2half_rn(s);
+  for (uint32_t i = 0; i < 8; ++i) part[row][col + i] = a[i];
+  __syncthreads();
+  if (tid < D / 2) {
+    // one accumulator per residue class p mod ROWS, classes added in increasing order
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (uint32_t r = 0; r < ROWS; ++r) {
+      s0 += part[r][2 * tid];
+      s1 += part[r][2 * tid + 1];
+    }
+    *reinterpret_cast<uint32_t *>(orow + 2 * tid) = pack_half2(s0, s1);
   }
 }
 
@@ -1275,8 +1409,8 @@ merge_partitions_warp_kernel(__half *__restrict__ out, const __half *__restrict_
                              uint32_t num_pairs, uint32_t max_num_partitions, uint32_t partition_size,
                              uint32_t ctx_limit, const uint32_t *__restrict__ table_offsets,
                              uint32_t block_shift) {
-  constexpr uint32_t DPL = D / 32;          // dims per lane: 4 or 2
-  constexpr uint32_t ROWS = 128 / (D / 4);  // residue classes of the CTA-per-pair kernel
+  constexpr uint32_t DPL = D / 32;                 // dims per lane: 4 or 2
+  constexpr uint32_t ROWS = MergeShape<D>::ROWS;   // residue classes of the CTA-per-pair kernel
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t work = blockIdx.x * 4 + (threadIdx.x >> 5); // (position in the launch) * num_heads + head
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

@@ -185,4 +185,28 @@ PA_API int pa_aid_measure_read_bandwidth(const void *buf, uint64_t bytes, const 
   return PA_OK;
 }
 
+PA_API int pa_aid_time_launches(pa_aid_launch_fn launch, const pa_params *params, uint32_t num_params,
+                                uint32_t calls, void *stream, float *us_per_call) {
+  if (launch == nullptr || params == nullptr || num_params == 0 || calls == 0 || us_per_call == nullptr)
+    return pa::fail(PA_ERR_BAD_ARG, "time_launches: null argument or zero count");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  PA_CUDA_TRY(cudaEventCreate(&t0));
+  PA_CUDA_TRY(cudaEventCreate(&t1));
+  int rc = PA_OK;
+  cudaError_t err = cudaEventRecord(t0, st);
+  for (uint32_t i = 0; i < calls && rc == PA_OK && err == cudaSuccess; ++i)
+    rc = launch(params + (i % num_params), stream, nullptr);
+  if (rc == PA_OK && err == cudaSuccess) err = cudaEventRecord(t1, st);
+  if (rc == PA_OK && err == cudaSuccess) err = cudaEventSynchronize(t1);
+  float ms = 0.f;
+  if (rc == PA_OK && err == cudaSuccess) err = cudaEventElapsedTime(&ms, t0, t1);
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
+  if (rc != PA_OK) return pa::fail(rc, "time_launches: the launcher returned %d", rc);
+  if (err != cudaSuccess) return pa::fail(PA_ERR_CUDA, "time_launches: %s", cudaGetErrorString(err));
+  *us_per_call = ms * 1000.f / static_cast<float>(calls);
+  return PA_OK;
+}
+
 } // extern "C"

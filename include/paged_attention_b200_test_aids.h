@@ -37,6 +37,17 @@ PA_API int pa_aid_selftest_wait_timeout(uint32_t limit_us, int32_t *status_word)
 PA_API int pa_aid_measure_read_bandwidth(const void *buf, uint64_t bytes, const void *buf2, uint64_t bytes2,
                                          uint32_t method, uint32_t iters, void *stream, float *gb_per_s);
 
+/* One of the product's four launchers (launch_kernels_loop and its siblings). */
+typedef int (*pa_aid_launch_fn)(const pa_params *p, void *stream, float *us_out);
+
+/* Times `calls` asynchronous calls of `launch`, issued back to back from C on `stream` between
+ * two CUDA events, call i with params[i % num_params] (e.g. one argument block per rotated
+ * KV-cache copy), and stores the mean microseconds per call.  This is the rate a C or C++ host
+ * of the library sees; a Python loop over the same calls adds its own microseconds per call,
+ * which matters for batches that take ten.  Blocks until done; allocates nothing on the device. */
+PA_API int pa_aid_time_launches(pa_aid_launch_fn launch, const pa_params *params, uint32_t num_params,
+                                uint32_t calls, void *stream, float *us_per_call);
+
 /* Message of the last non-PA_OK return of this library on the calling thread. */
 PA_API const char *pa_aid_last_error(void);
 
