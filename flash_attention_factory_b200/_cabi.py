@@ -39,6 +39,9 @@ EXPORTED_SYMBOLS = (
     "pa_decode_step_host_batch",
     "pa_split_by_kv_length",
     "pa_host_batch_plan",
+    "pa_split_lpt",
+    "pa_multi_gpu_run",
+    "pa_multi_gpu_gather_out",
     "pa_version",
 )
 
@@ -149,6 +152,33 @@ class PaHostBatch(ctypes.Structure):
 
 STEP_LAST_OUT_DIRECT = 1
 
+
+class PaDeviceShard(ctypes.Structure):
+    """struct pa_device_shard of include/paged_attention_b200.h."""
+
+    _fields_ = [("device", ctypes.c_int32), ("entry", ctypes.c_int32), ("params", PaParams)]
+
+
+SHARD_LAUNCH_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_int32, ctypes.POINTER(PaParams), ctypes.c_void_p,
+                                   ctypes.c_void_p)
+
+
+class PaMultiGpuOptions(ctypes.Structure):
+    """struct pa_multi_gpu_options of include/paged_attention_b200.h."""
+
+    _fields_ = [
+        ("calls", ctypes.c_uint32),
+        ("warmup", ctypes.c_uint32),
+        ("flags", ctypes.c_uint32),
+        ("reserved", ctypes.c_uint32),
+        ("launch", SHARD_LAUNCH_FN),
+        ("user", ctypes.c_void_p),
+    ]
+
+
+MULTI_GPU_HOST_ONLY = 1
+GATHER_BY_SEQUENCE, GATHER_BY_KV_HEAD = 0, 1
+
 ENTRY_IDS = {"launch_kernels_loop": 0, "launch_kernels_reduce": 1, "launch_kernels_fp8_loop": 2,
              "launch_kernels_fp8_reduce": 3}
 
@@ -205,6 +235,15 @@ def load_library() -> ctypes.CDLL:
                                        ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint64),
                                        ctypes.POINTER(ctypes.c_uint64)]
     lib.pa_host_batch_plan.restype = ctypes.c_int
+    lib.pa_split_lpt.argtypes = [ctypes.POINTER(ctypes.c_uint32), ctypes.c_uint32, ctypes.c_uint32,
+                                 ctypes.POINTER(ctypes.c_uint32)]
+    lib.pa_split_lpt.restype = ctypes.c_int
+    lib.pa_multi_gpu_run.argtypes = [ctypes.POINTER(PaDeviceShard), ctypes.c_uint32, ctypes.POINTER(PaMultiGpuOptions),
+                                     ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float)]
+    lib.pa_multi_gpu_run.restype = ctypes.c_int
+    lib.pa_multi_gpu_gather_out.argtypes = [ctypes.POINTER(PaDeviceShard), ctypes.c_uint32, ctypes.c_int32,
+                                            ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint32]
+    lib.pa_multi_gpu_gather_out.restype = ctypes.c_int
     lib.pa_split_by_kv_length.argtypes = [ctypes.POINTER(ctypes.c_uint32), ctypes.c_uint32, ctypes.c_uint32,
                                           ctypes.POINTER(ctypes.c_uint32)]
     lib.pa_split_by_kv_length.restype = ctypes.c_int
@@ -250,6 +289,18 @@ def split_by_kv_length(context_lens, parts: int) -> list[tuple[int, int]]:
     bounds = (ctypes.c_uint32 * (parts + 1))()
     check(load_library().pa_split_by_kv_length(arr, len(lens), parts, bounds))
     return [(int(bounds[r]), int(bounds[r + 1])) for r in range(parts)]
+
+
+def split_lpt(context_lens, parts: int) -> list[list[int]]:
+    """Sequence ids per part, longest first to the lightest part (pa_split_lpt); ids ascending."""
+    lens = [int(c) for c in context_lens]
+    arr = (ctypes.c_uint32 * max(1, len(lens)))(*lens)
+    part_of = (ctypes.c_uint32 * max(1, len(lens)))()
+    check(load_library().pa_split_lpt(arr, len(lens), parts, part_of))
+    shards = [[] for _ in range(parts)]
+    for i in range(len(lens)):
+        shards[int(part_of[i])].append(i)
+    return shards
 
 
 def launch(entry: str, params: PaParams, stream: int, timed: bool) -> list[float]:

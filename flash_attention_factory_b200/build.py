@@ -28,6 +28,7 @@ SOURCES = [
     "host_common.cu",
     "c_api.cu",
     "host_step.cu",
+    "multi_gpu.cu",
     "launch_kernels_loop.cu",
     "launch_kernels_reduce.cu",
     "launch_kernels_fp8_loop.cu",

@@ -175,7 +175,7 @@ inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_cou
   if (context_hint(p) != 0) {
     // a CTA should own at least kMinStagesPerCta stages of the longest context: below that the
     // cluster merge and the extra CTAs cost more than the split saves
-    constexpr uint32_t kMinStagesPerCta = 4;
+    constexpr uint32_t kMinStagesPerCta = 2;
     const uint32_t stages = divide_round_up(context_hint(p), tokens_per_stage);
     while (cs > 1 && stages / cs < kMinStagesPerCta) --cs;
   }

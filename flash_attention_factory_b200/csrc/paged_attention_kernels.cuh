@@ -1276,16 +1276,16 @@ __device__ __forceinline__ uint32_t merge_context(const uint32_t *context_lens, 
 //   out[d] = sum_p (w_p / W) * tmp_out[p, d]
 // over the partitions p < ceil(ctx / partition_size) only
 // (reference paged_attention_kernel_v2.hpp:679,736-764,813-863,924-932).
-// Latency-bound: a thread owns 8 dims (one 16-byte load) of kMergeUnroll partial rows, which
+// Latency-bound: a thread owns 4 dims (one 8-byte load) of kMergeUnroll partial rows, which
 // are requested together with the statistics, before the weights are known; up to
 // kMergeUnroll * ROWS partitions (64 for head size 128: a context of 32768 tokens) cost one
 // memory round trip after the context length has arrived.
-constexpr uint32_t kMergeUnroll = 8; // partial rows in flight per thread
+constexpr uint32_t kMergeUnroll = 16; // partial rows in flight per thread
 
 template <int D>
 struct MergeShape {
-  static constexpr uint32_t LANES_PER_ROW = D / 8;        // each lane owns 8 dims (16 bytes)
-  static constexpr uint32_t ROWS = 128 / LANES_PER_ROW;   // partitions handled in parallel: 8 or 16
+  static constexpr uint32_t LANES_PER_ROW = D / 4;        // each lane owns 4 dims (8 bytes)
+  static constexpr uint32_t ROWS = 128 / LANES_PER_ROW;   // partitions handled in parallel: 4 or 8
 };
 
 template <int D>
@@ -1316,18 +1316,21 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
   __shared__ float part[ROWS][D];
 
   const uint32_t row = tid / LANES_PER_ROW;
-  const uint32_t col = (tid % LANES_PER_ROW) * 8;
+  const uint32_t col = (tid % LANES_PER_ROW) * 4;
   // first UNROLL rows of this thread: requested now, used after the weights are ready
-  uint4 raw[UNROLL];
+  uint2 raw[UNROLL];
 #pragma unroll
   for (uint32_t u = 0; u < UNROLL; ++u) {
     const uint32_t p = row + u * ROWS;
-    raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint4 *>(tmp_out + (base + p) * D + col)) : make_uint4(0u, 0u, 0u, 0u);
+    raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint2 *>(tmp_out + (base + p) * D + col)) : make_uint2(0u, 0u);
   }
 
-  // global max over partitions
-  float m = neg_infinity();
-  for (uint32_t p = tid; p < np; p += 128) m = fmaxf(m, max_logits[base + p]);
+  // global max over partitions; the first 128 partitions' statistics stay in registers, so
+  // the weights below need no second trip to memory
+  const float ml_own = (tid < np) ? max_logits[base + tid] : neg_infinity();
+  const float es_own = (tid < np) ? exp_sums[base + tid] : 0.f;
+  float m = ml_own;
+  for (uint32_t p = tid + 128; p < np; p += 128) m = fmaxf(m, max_logits[base + p]);
 #pragma unroll
   for (uint32_t o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if ((tid & 31u) == 0) red[tid >> 5] = m;
@@ -1336,7 +1339,12 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
   __syncthreads();
   // rescaled weights and their total
   float wsum = 0.f;
-  for (uint32_t p = tid; p < np; p += 128) {
+  if (tid < np) {
+    const float w = es_own * __expf(ml_own - m);
+    weights[tid] = w;
+    wsum = w;
+  }
+  for (uint32_t p = tid + 128; p < np; p += 128) {
     const float w = exp_sums[base + p] * __expf(max_logits[base + p] - m);
     if (p < WEIGHT_CACHE) weights[p] = w;
     wsum += w;
@@ -1351,15 +1359,14 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
     return (p < WEIGHT_CACHE) ? weights[p] : exp_sums[base + p] * __expf(max_logits[base + p] - m);
   };
 
-  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  auto accumulate = [&](const uint4 &v, float w) {
-    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (uint32_t i = 0; i < 4; ++i) {
-      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&words[i]));
-      a[2 * i] += w * f.x;
-      a[2 * i + 1] += w * f.y;
-    }
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  auto accumulate = [&](uint2 v, float w) {
+    const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
+    const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
+    a0 += w * v01.x;
+    a1 += w * v01.y;
+    a2 += w * v23.x;
+    a3 += w * v23.y;
   };
   // partitions are taken in increasing order per thread: the sum has a fixed order
 #pragma unroll
@@ -1371,7 +1378,7 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
 #pragma unroll
     for (uint32_t u = 0; u < UNROLL; ++u) {
       const uint32_t p = p0 + u * ROWS;
-      raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint4 *>(tmp_out + (base + p) * D + col)) : make_uint4(0u, 0u, 0u, 0u);
+      raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint2 *>(tmp_out + (base + p) * D + col)) : make_uint2(0u, 0u);
     }
 #pragma unroll
     for (uint32_t u = 0; u < UNROLL; ++u) {
@@ -1379,8 +1386,10 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
       if (p < np) accumulate(raw[u], weight_of(p) * inv_w);
     }
   }
-#pragma unroll
-  for (uint32_t i = 0; i < 8; ++i) part[row][col + i] = a[i];
+  part[row][col] = a0;
+  part[row][col + 1] = a1;
+  part[row][col + 2] = a2;
+  part[row][col + 3] = a3;
   __syncthreads();
   if (tid < D / 2) {
     // one accumulator per residue class p mod ROWS, classes added in increasing order

@@ -282,6 +282,62 @@ PA_API int pa_decode_step_host_batch(int32_t entry, const pa_params *p, const pa
 PA_API int pa_host_batch_plan(const pa_params *p, const pa_host_batch *io, uint32_t *sub_batches,
                               uint64_t *h2d_bytes, uint64_t *d2h_bytes);
 
+/* ---- several GPUs in one process (no reference counterpart: the reference is single-device,
+ * paged_attention_loop/launch_kernels_loop.h:32-34) ---- */
+
+/* Deals num_seqs sequences to `parts` parts, longest first, each to the part that holds the
+ * fewest KV tokens so far (ties: lower sequence id, lower part): part_of[i] is the part of
+ * sequence i.  Balanced to within a fraction of one sequence where consecutive ranges
+ * (pa_split_by_kv_length) can be off by a whole long sequence. */
+PA_API int pa_split_lpt(const uint32_t *context_lens, uint32_t num_seqs, uint32_t parts, uint32_t *part_of);
+
+/* One shard of a batch: its GPU, its entry point and its argument block, whose pointers all
+ * live on that GPU.  A shard by sequence holds some of the sequences with all heads; a shard
+ * by KV head holds all sequences with num_kv_heads / N heads of both caches, the matching
+ * query heads and the matching slice of `out`. */
+typedef struct pa_device_shard {
+  int32_t device; /* CUDA device ordinal */
+  int32_t entry;  /* pa_entry */
+  pa_params params;
+} pa_device_shard;
+
+/* Launcher of one shard; the default calls the library's own entry point for shard->entry. */
+typedef int (*pa_shard_launch_fn)(int32_t entry, const pa_params *p, void *stream, void *user);
+
+/* Run without any CUDA call (host threads, barrier and aggregation only; host-clock timing):
+ * for tests of the driver logic on machines without a GPU, together with a `launch` stand-in. */
+#define PA_MULTI_GPU_HOST_ONLY 1u
+
+typedef struct pa_multi_gpu_options {
+  uint32_t calls;            /* calls per shard inside the timed region, at least 1 */
+  uint32_t warmup;           /* untimed calls per shard before the common start */
+  uint32_t flags;            /* PA_MULTI_GPU_* */
+  uint32_t reserved;
+  pa_shard_launch_fn launch; /* NULL = the library's entry points */
+  void *user;                /* passed to `launch` */
+} pa_multi_gpu_options;
+
+/* Runs the shards of one batch at the same time from this process: one host thread and one
+ * stream per shard, `warmup` untimed calls each, a common start barrier, then `calls`
+ * asynchronous calls per shard timed with CUDA events on the shard's stream.  Stores the mean
+ * microseconds per call of the slowest shard (max over shards; the time of the whole batch) and,
+ * if us_per_call_each is not NULL, of every shard.  There is no exchange between the shards.  If
+ * shards fail, the others still finish; the call returns the first failing shard's code and
+ * pa_last_error() names every failing shard.  Blocks until all shards are done.  Several shards
+ * may name the same device (they then share it through separate streams). */
+PA_API int pa_multi_gpu_run(const pa_device_shard *shards, uint32_t num_shards, const pa_multi_gpu_options *options,
+                            float *us_per_call_max, float *us_per_call_each);
+
+#define PA_GATHER_BY_SEQUENCE 0 /* shard i's rows follow those of shard i - 1 in dst */
+#define PA_GATHER_BY_KV_HEAD 1  /* shard i's heads follow those of shard i - 1 in every row of dst */
+
+/* Collects the shards' `out` tensors into dst [sum of num_seqs, num_heads, head_size] (by
+ * sequence) or [num_seqs, dst_num_heads, head_size] (by KV head) on dst_device, with peer
+ * copies, after the shards' work is done; blocks until the copies have finished.  The only
+ * cross-GPU step of the path and not part of any timed region. */
+PA_API int pa_multi_gpu_gather_out(const pa_device_shard *shards, uint32_t num_shards, int32_t mode,
+                                   void *dst, int32_t dst_device, uint32_t dst_num_heads);
+
 /* Arguments of pa_reshape_and_cache. */
 typedef struct pa_cache_write_params {
   const void *key;             /* fp16 [num_tokens, num_kv_heads, head_size] */
