@@ -653,11 +653,13 @@ def timeline_report(w: Workload, calls: int) -> None:
     t = t[t[:, 0] > newest - 5e6]
     t0 = t[:, 0].min()
     names = ["entry", "after_wait_for_previous_kernel", "first_copy_issued", "first_stage_complete",
-             "last_stage_consumed", "exit"]
+             "last_stage_consumed", "exit", None, "cluster_met_for_merge"]
     print(f"{w.spec['name']} {variant}: {t.size(0)} CTAs, kernel span "
           f"{(t[:, 5].max() - t0) / 1e3:.1f} us, KV bytes {w.kv_bytes}")
     print(f"{'event (us after first entry)':34s} {'min':>8s} {'p10':>8s} {'median':>8s} {'p90':>8s} {'max':>8s}")
     for k, name in enumerate(names):
+        if name is None:
+            continue
         col = t[:, k]
         col = (col[col > 0] - t0) / 1e3
         if col.numel() == 0:

@@ -79,7 +79,7 @@ inline uint32_t next_sched_slot(bool capturing) {
 // for the launch ramp and the tail of a launch.  One row per CTA of the most recent launch of
 // this translation unit: [0] kernel entry, [1] after the wait for the previous kernel,
 // [2] first copy issued, [3] first stage complete, [4] last stage of the last item consumed,
-// [5] exit, [6] work items done, [7] SM id.
+// [5] exit, [6] work items done, [7] loop mode: the cluster has met for the merge (else 0).
 #ifdef PA_TIMELINE
 constexpr uint32_t kTimelineCtas = 4096;
 static __device__ unsigned long long g_timeline[kTimelineCtas][8];
@@ -319,6 +319,102 @@ __device__ __forceinline__ void load_q_fragments(uint32_t (&qf)[D / 16][2], cons
   }
 }
 
+// Loop mode: merge of the partial results that the warps of a cluster have parked in their
+// shared memory (per warp: O[8][D], then m[8], then l[8], WARP_AREA floats apart), through
+// distributed shared memory.
+//
+// A unit of the merge is one output row (KV head hh of the CTA's group, query column g) times
+// one chunk of 32 dims.  Unit u belongs to CTA u mod num_ranks and, there, to warp
+// (u / num_ranks) mod NW.  The sources of a row are the R = num_ranks * slices warps that hold a
+// part of its tokens; lane j of the merging warp fetches source j's (m, l), so the row
+// statistics take one round trip, and the partial rows of UB units from JB sources each are
+// requested together before the first is used.  All sums run in a fixed order.
+template <int D, uint32_t NW, uint32_t WARP_AREA, uint32_t UB, uint32_t JB>
+__device__ __noinline__ void merge_cluster_rows(float *areas, __half *out, const float *v_scale_per_head,
+                                                float out_scale, uint32_t G, uint32_t num_heads, uint32_t seq,
+                                                uint32_t head_base, uint32_t hpc, uint32_t cta_rank,
+                                                uint32_t num_ranks, uint32_t cw, uint32_t lane, bool ok) {
+  const cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+  const uint32_t slices = NW / hpc;           // 1, 2 or 4: a power of two
+  const uint32_t slice_shift = 31u - __clz(slices);
+  const uint32_t R = num_ranks * slices;      // <= 8 * 4 = 32
+  constexpr uint32_t CHUNKS = D / 32;
+  const uint32_t units = hpc * G * CHUNKS;
+  // lane j < R looks at source j: warp (j mod slices) of the row's head in CTA j / slices
+  const float *lane_src = cluster.map_shared_rank(areas, (lane < R) ? (lane >> slice_shift) : 0u) +
+                          (lane & (slices - 1u)) * WARP_AREA;
+#pragma unroll 1
+  for (uint32_t k0 = cw; cta_rank + num_ranks * k0 < units; k0 += NW * UB) {
+    uint32_t row_g[UB], head_area[UB], chunk[UB], kv_head[UB];
+    bool valid[UB];
+    float f[UB], l_all[UB], m_src[UB], l_src[UB];
+#pragma unroll
+    for (uint32_t q = 0; q < UB; ++q) {
+      const uint32_t u = cta_rank + num_ranks * (k0 + q * NW);
+      valid[q] = u < units;
+      const uint32_t row = valid[q] ? u / CHUNKS : 0u;
+      chunk[q] = valid[q] ? u % CHUNKS : 0u;
+      const uint32_t hh = row / G;
+      row_g[q] = row - hh * G;
+      kv_head[q] = head_base + hh;
+      head_area[q] = (hh << slice_shift) * WARP_AREA; // first warp area of the row's head
+      m_src[q] = neg_infinity();
+      l_src[q] = 0.f;
+      if (valid[q] && lane < R) {
+        const float *pa = lane_src + head_area[q] + 8 * D;
+        m_src[q] = pa[row_g[q]];
+        l_src[q] = pa[8 + row_g[q]];
+      }
+    }
+#pragma unroll
+    for (uint32_t q = 0; q < UB; ++q) {
+      float m_all = m_src[q];
+#pragma unroll
+      for (uint32_t o = 16; o > 0; o >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
+      f[q] = (m_src[q] == neg_infinity()) ? 0.f : fast_exp2(m_src[q] - m_all);
+      float l_sum = f[q] * l_src[q];
+#pragma unroll
+      for (uint32_t o = 16; o > 0; o >>= 1) l_sum += __shfl_xor_sync(0xffffffffu, l_sum, o);
+      l_all[q] = l_sum;
+    }
+    float o_all[UB];
+#pragma unroll
+    for (uint32_t q = 0; q < UB; ++q) o_all[q] = 0.f;
+#pragma unroll 1
+    for (uint32_t j0 = 0; j0 < R; j0 += JB) {
+      float v[UB][JB];
+#pragma unroll
+      for (uint32_t jj = 0; jj < JB; ++jj) {
+        const uint32_t j = j0 + jj;
+        const float *pj = cluster.map_shared_rank(areas, (j < R) ? (j >> slice_shift) : 0u) +
+                          (j & (slices - 1u)) * WARP_AREA;
+#pragma unroll
+        for (uint32_t q = 0; q < UB; ++q)
+          v[q][jj] = (valid[q] && j < R) ? pj[head_area[q] + row_g[q] * D + chunk[q] * 32 + lane] : 0.f;
+      }
+#pragma unroll
+      for (uint32_t jj = 0; jj < JB; ++jj) {
+#pragma unroll
+        for (uint32_t q = 0; q < UB; ++q) {
+          const float fj = __shfl_sync(0xffffffffu, f[q], (j0 + jj) & 31u);
+          if (j0 + jj < R) o_all[q] += fj * v[q][jj];
+        }
+      }
+    }
+#pragma unroll
+    for (uint32_t q = 0; q < UB; ++q) {
+      if (valid[q] && ok) {
+        // acc * (1 / l) as the reference does (paged_attention_utils.hpp:834-835);
+        // an empty context (l = 0) gives zeros
+        const float inv = (l_all[q] > 0.f) ? (1.f / l_all[q]) : 0.f;
+        const size_t head = static_cast<size_t>(seq) * num_heads + kv_head[q] * G + row_g[q];
+        const float head_scale = (v_scale_per_head != nullptr) ? __ldg(v_scale_per_head + kv_head[q]) : out_scale;
+        out[head * D + chunk[q] * 32 + lane] = __float2half_rn(o_all[q] * head_scale * inv);
+      }
+    }
+  }
+}
+
 template <int D, int KV, int MODE, int NWARPS = 4>
 __global__ void __launch_bounds__(paged_attention_policy_v2<D, KV, NWARPS>::threads_per_cta,
                                   paged_attention_policy_v2<D, KV, NWARPS>::ctas_per_sm)
@@ -355,14 +451,12 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
 #ifdef PA_TIMELINE
   const uint32_t timeline_cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
   if (threadIdx.x == 32) {
-    uint32_t smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
     PA_STAMP(0);
     PA_STAMP_VALUE(2, 0ull);
     PA_STAMP_VALUE(3, 0ull);
     PA_STAMP_VALUE(4, 0ull);
     PA_STAMP_VALUE(6, 0ull);
-    PA_STAMP_VALUE(7, static_cast<unsigned long long>(smid));
+    PA_STAMP_VALUE(7, 0ull);
   }
 #endif
 
@@ -1146,99 +1240,25 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     cg::cluster_group cluster = cg::this_cluster();
     if (num_ranks == 1) __syncthreads(); // a lone CTA has no peer to wait for
     else cluster.sync();
+    if (threadIdx.x == 32) PA_STAMP(7);
     if (warp != 0) {
-      // A unit of the merge is one output row (KV head hh of the CTA's group, query column g)
-      // times one chunk of 32 dims.  Unit u belongs to CTA u mod num_ranks and, there, to warp
-      // (u / num_ranks) mod NW.  The sources of a row are the R = num_ranks * slices warps that
-      // hold a part of its tokens; lane j of the merging warp fetches source j's (m, l), so the
-      // row statistics take one round trip through distributed shared memory, and the R partial
-      // rows of a chunk are requested together before the first is used: a warp's units cost
-      // two round trips, not two per source.  All sums run in a fixed order.
-      const uint32_t G = args.group;
+      // with few sources per row, more rows are merged per pass (16 partial rows in flight per
+      // lane either way)
+      const uint32_t sources = num_ranks * (NW / hpc);
       const bool ok = (*abort_flag == 0u);
-      const uint32_t cw = warp - 1;
-      const uint32_t slices = NW / hpc;
-      const uint32_t R = num_ranks * slices; // <= 8 * 4 = 32
-      constexpr uint32_t CHUNKS = D / 32;
-      constexpr uint32_t UB = 4; // units of one pass
-      const uint32_t units = hpc * G * CHUNKS;
       float *areas = reinterpret_cast<float *>(smem);
-      const float *lane_src = cluster.map_shared_rank(areas, (lane < R) ? lane / slices : 0u) +
-                              (lane % slices) * L::WARP_AREA_FLOATS;
-      for (uint32_t k0 = cw; cta_rank + num_ranks * k0 < units; k0 += NW * UB) {
-        uint32_t row_g[UB], row_hh[UB], chunk[UB];
-        bool valid[UB];
-        float f[UB], l_all[UB];
-#pragma unroll
-        for (uint32_t q = 0; q < UB; ++q) {
-          const uint32_t u = cta_rank + num_ranks * (k0 + q * NW);
-          valid[q] = u < units;
-          const uint32_t row = valid[q] ? u / CHUNKS : 0u;
-          chunk[q] = valid[q] ? u % CHUNKS : 0u;
-          row_hh[q] = row / G;
-          row_g[q] = row - row_hh[q] * G;
-        }
-        float m_src[UB], l_src[UB];
-#pragma unroll
-        for (uint32_t q = 0; q < UB; ++q) {
-          m_src[q] = neg_infinity();
-          l_src[q] = 0.f;
-          if (valid[q] && lane < R) {
-            const float *pa = lane_src + row_hh[q] * slices * L::WARP_AREA_FLOATS + 8 * D;
-            m_src[q] = pa[row_g[q]];
-            l_src[q] = pa[8 + row_g[q]];
-          }
-        }
-#pragma unroll
-        for (uint32_t q = 0; q < UB; ++q) {
-          float m_all = m_src[q];
-#pragma unroll
-          for (uint32_t o = 16; o > 0; o >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
-          f[q] = (m_src[q] == neg_infinity()) ? 0.f : fast_exp2(m_src[q] - m_all);
-          float l_sum = f[q] * l_src[q];
-#pragma unroll
-          for (uint32_t o = 16; o > 0; o >>= 1) l_sum += __shfl_xor_sync(0xffffffffu, l_sum, o);
-          l_all[q] = l_sum;
-        }
-        float o_all[UB] = {0.f, 0.f, 0.f, 0.f};
-        for (uint32_t j0 = 0; j0 < R; j0 += 8) {
-          float v[UB][8];
-#pragma unroll
-          for (uint32_t q = 0; q < UB; ++q) {
-#pragma unroll
-            for (uint32_t jj = 0; jj < 8; ++jj) {
-              const uint32_t j = j0 + jj;
-              v[q][jj] = 0.f;
-              if (valid[q] && j < R) {
-                const float *pj = cluster.map_shared_rank(areas, j / slices) +
-                                  (row_hh[q] * slices + j % slices) * L::WARP_AREA_FLOATS;
-                v[q][jj] = pj[row_g[q] * D + chunk[q] * 32 + lane];
-              }
-            }
-          }
-#pragma unroll
-          for (uint32_t q = 0; q < UB; ++q) {
-#pragma unroll
-            for (uint32_t jj = 0; jj < 8; ++jj) {
-              const float fj = __shfl_sync(0xffffffffu, f[q], (j0 + jj) & 31u);
-              if (j0 + jj < R) o_all[q] += fj * v[q][jj];
-            }
-          }
-        }
-#pragma unroll
-        for (uint32_t q = 0; q < UB; ++q) {
-          if (valid[q] && ok) {
-            // acc * (1 / l) as the reference does (paged_attention_utils.hpp:834-835);
-            // an empty context (l = 0) gives zeros
-            const float inv = (l_all[q] > 0.f) ? (1.f / l_all[q]) : 0.f;
-            const uint32_t kv_head = first.head_base + row_hh[q];
-            const size_t head = static_cast<size_t>(first.seq) * args.num_heads + kv_head * G + row_g[q];
-            const float head_scale = (args.v_scale_per_head != nullptr) ? __ldg(args.v_scale_per_head + kv_head)
-                                                                        : args.out_scale;
-            args.out[head * D + chunk[q] * 32 + lane] = __float2half_rn(o_all[q] * head_scale * inv);
-          }
-        }
-      }
+      if (sources <= 2)
+        merge_cluster_rows<D, NW, L::WARP_AREA_FLOATS, 8, 2>(areas, args.out, args.v_scale_per_head, args.out_scale, args.group,
+                                                                   args.num_heads, first.seq, first.head_base, hpc, cta_rank,
+                                                                   num_ranks, warp - 1, lane, ok);
+      else if (sources <= 4)
+        merge_cluster_rows<D, NW, L::WARP_AREA_FLOATS, 4, 4>(areas, args.out, args.v_scale_per_head, args.out_scale, args.group,
+                                                                   args.num_heads, first.seq, first.head_base, hpc, cta_rank,
+                                                                   num_ranks, warp - 1, lane, ok);
+      else
+        merge_cluster_rows<D, NW, L::WARP_AREA_FLOATS, 2, 8>(areas, args.out, args.v_scale_per_head, args.out_scale, args.group,
+                                                                   args.num_heads, first.seq, first.head_base, hpc, cta_rank,
+                                                                   num_ranks, warp - 1, lane, ok);
     }
     if (num_ranks > 1) cluster.sync(); // peers may still be reading this CTA's shared memory
   }
