@@ -182,9 +182,52 @@ inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_cou
   return cs;
 }
 
-template <int D, int KV, int NWARPS = 4>
-AttnArgs make_attn_args(const pa_params *p, bool loop_mode = false, int sm_count = 0) {
-  using policy = paged_attention_policy_v2<D, KV, NWARPS>;
+// KV heads per CTA: with 4 (8 in the wide CTA) a warp owns a head and nothing is merged across
+// warps; fewer when the head count does not divide.
+inline uint32_t choose_heads_per_cta(const pa_params *p, bool wide, bool loop_mode, int sm_count) {
+  if (wide) return 8u; // the wide CTA is only chosen for num_kv_heads % 8 == 0: a warp per head
+  uint32_t hpc = (p->num_kv_heads % 4 == 0) ? 4u : ((p->num_kv_heads % 2 == 0) ? 2u : 1u);
+#ifdef PA_TUNING_KNOBS
+  {
+    // tuning build only: PA_FORCE_HPC=1|2 lowers the number of KV heads per CTA
+    static const int forced = [] {
+      const char *e = std::getenv("PA_FORCE_HPC");
+      return e ? std::atoi(e) : 0;
+    }();
+    if ((forced == 1 || forced == 2) && static_cast<uint32_t>(forced) < hpc) hpc = forced;
+  }
+#endif
+  // The loop variant has one cluster of at most 8 CTAs per (sequence, head group): with very
+  // few sequences, fewer heads per CTA (warps then split the tokens of a head) is the only
+  // way to put a CTA on every SM
+  if (loop_mode)
+    while (hpc > 1 && static_cast<uint64_t>(p->num_seqs) * (p->num_kv_heads / hpc) * 8ull <
+                          static_cast<uint64_t>(sm_count))
+      hpc /= 2;
+  return hpc;
+}
+
+// Largest number of tiles per warp and stage for which the kernel is built, per (head size, KV
+// type): the stage must stay at 32 KB or less so that the ring keeps three of them.
+template <int D, int KV>
+constexpr uint32_t max_stage_tiles() {
+  return (KV == KV_F16) ? (D == 128 ? 1u : 2u) : (D == 128 ? 2u : 4u);
+}
+
+// Tiles per warp and stage for one launch: as many as let one TMA box still fill a head's rows
+// of the stage, i.e. 16 * slices * tiles <= block_size (slices = warps per head).  KV blocks of 16
+// tokens keep one tile; blocks of 32 and more get boxes of up to 16 KB.
+template <int D, int KV>
+uint32_t choose_stage_tiles(const pa_params *p, uint32_t hpc, uint32_t consumer_warps) {
+  const uint32_t step_tokens = 16u * (consumer_warps / hpc);
+  uint32_t tiles = max_stage_tiles<D, KV>();
+  while (tiles > 1u && step_tokens * tiles > p->block_size) tiles /= 2u;
+  return tiles;
+}
+
+template <int D, int KV, int NWARPS = 4, int TILES = 1>
+AttnArgs make_attn_args(const pa_params *p, uint32_t hpc) {
+  using policy = paged_attention_policy_v2<D, KV, NWARPS, TILES>;
   AttnArgs a{};
   a.query = static_cast<const __half *>(p->query);
   a.out = static_cast<__half *>(p->out);
@@ -203,28 +246,7 @@ AttnArgs make_attn_args(const pa_params *p, bool loop_mode = false, int sm_count
   a.block_shift = log2_pow2(p->block_size);
   a.ctx_limit = context_limit(p);
   a.table_offsets = p->block_table_offsets;
-  // KV heads per CTA: with 4 a warp owns a head and nothing is merged across warps
-  a.hpc = (p->num_kv_heads % 4 == 0) ? 4u : ((p->num_kv_heads % 2 == 0) ? 2u : 1u);
-  if (NWARPS == 8) {
-    a.hpc = 8u; // the wide CTA is only chosen for num_kv_heads % 8 == 0: a warp per head
-  }
-#ifdef PA_TUNING_KNOBS
-  else {
-    // tuning build only: PA_FORCE_HPC=1|2 lowers the number of KV heads per CTA
-    static const int forced = [] {
-      const char *e = std::getenv("PA_FORCE_HPC");
-      return e ? std::atoi(e) : 0;
-    }();
-    if ((forced == 1 || forced == 2) && static_cast<uint32_t>(forced) < a.hpc) a.hpc = forced;
-  }
-#endif
-  // The loop variant has one cluster of at most 8 CTAs per (sequence, head group): with very
-  // few sequences, fewer heads per CTA (warps then split the tokens of a head) is the only
-  // way to put a CTA on every SM
-  if (loop_mode)
-    while (a.hpc > 1 && static_cast<uint64_t>(p->num_seqs) * (p->num_kv_heads / a.hpc) * 8ull <
-                            static_cast<uint64_t>(sm_count))
-      a.hpc /= 2;
+  a.hpc = hpc;
   a.tokens_per_stage = policy::tokens_per_stage / a.hpc;
   a.rows_per_box = p->block_size < a.tokens_per_stage ? p->block_size : a.tokens_per_stage;
   a.boxes_per_stage = a.hpc * (a.tokens_per_stage / a.rows_per_box);
@@ -244,17 +266,18 @@ AttnArgs make_attn_args(const pa_params *p, bool loop_mode = false, int sm_count
   return a;
 }
 
-// Enqueues the attention kernel of one (D, KV, MODE) instantiation.
-template <int D, int KV, int MODE, int NWARPS = 4>
-int enqueue_attention(const pa_params *p, cudaStream_t stream) {
+// Enqueues the attention kernel of one (D, KV, MODE, CTA shape, stage size) instantiation.
+template <int D, int KV, int MODE, int NWARPS = 4, int TILES = 1>
+int enqueue_attention(const pa_params *p, cudaStream_t stream, uint32_t hpc) {
   static_assert(NWARPS == 4 || MODE == MODE_SPLIT, "the wide CTA exists for the split variant only");
-  using L = SmemLayout<D, KV, NWARPS>;
+  static_assert(NWARPS == 4 || TILES == 1, "the wide CTA is built with one tile per stage");
+  using L = SmemLayout<D, KV, NWARPS, TILES>;
   using policy = typename L::policy;
   DeviceInfo dev{};
   if (int rc = get_device_info(&dev)) return rc;
   if (dev.cc_major < 10) return fail(PA_ERR_CUDA, "this library needs an sm_100a device");
 
-  AttnArgs args = make_attn_args<D, KV, NWARPS>(p, MODE == MODE_LOOP, dev.sm_count);
+  AttnArgs args = make_attn_args<D, KV, NWARPS, TILES>(p, hpc);
   if (MODE == MODE_SPLIT) {
     // one allocator per translation unit, like the counter table it indexes
     cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
@@ -265,7 +288,7 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream) {
   if (int rc = encode_cache_map<D, KV>(&map_k, p->key_cache, p, args.rows_per_box, args.heads_per_box)) return rc;
   if (int rc = encode_cache_map<D, KV>(&map_v, p->value_cache, p, args.rows_per_box, args.heads_per_box)) return rc;
 
-  auto kernel = paged_attention_kernel<D, KV, MODE, NWARPS>;
+  auto kernel = paged_attention_kernel<D, KV, MODE, NWARPS, TILES>;
   static thread_local int configured_device = -1;
   int device = 0;
   PA_CUDA_TRY(cudaGetDevice(&device));
@@ -415,17 +438,33 @@ bool wants_wide_cta(const pa_params *p) {
   return items >= 2ull * static_cast<uint64_t>(dev.sm_count);
 }
 
+// stage-size dispatch for one head size, KV type and mode (default CTA shape)
+template <int D, int KV, int MODE>
+int dispatch_stage_tiles(const pa_params *p, cudaStream_t stream) {
+  DeviceInfo dev{};
+  if (int rc = get_device_info(&dev)) return rc;
+  const uint32_t hpc = choose_heads_per_cta(p, /*wide=*/false, MODE == MODE_LOOP, dev.sm_count);
+  const uint32_t tiles = choose_stage_tiles<D, KV>(p, hpc, 4u);
+  if constexpr (max_stage_tiles<D, KV>() >= 4u) {
+    if (tiles == 4u) return enqueue_attention<D, KV, MODE, 4, 4>(p, stream, hpc);
+  }
+  if constexpr (max_stage_tiles<D, KV>() >= 2u) {
+    if (tiles >= 2u) return enqueue_attention<D, KV, MODE, 4, 2>(p, stream, hpc);
+  }
+  return enqueue_attention<D, KV, MODE, 4, 1>(p, stream, hpc);
+}
+
 // head-size dispatch for one KV type and mode
 template <int KV, int MODE>
 int dispatch_head_size(const pa_params *p, cudaStream_t stream) {
   if constexpr (KV != KV_F16 && MODE == MODE_SPLIT) {
     if (wants_wide_cta<KV, MODE>(p)) {
-      if (p->head_size == 128) return enqueue_attention<128, KV, MODE, 8>(p, stream);
-      return enqueue_attention<64, KV, MODE, 8>(p, stream);
+      if (p->head_size == 128) return enqueue_attention<128, KV, MODE, 8>(p, stream, 8u);
+      return enqueue_attention<64, KV, MODE, 8>(p, stream, 8u);
     }
   }
-  if (p->head_size == 128) return enqueue_attention<128, KV, MODE>(p, stream);
-  return enqueue_attention<64, KV, MODE>(p, stream);
+  if (p->head_size == 128) return dispatch_stage_tiles<128, KV, MODE>(p, stream);
+  return dispatch_stage_tiles<64, KV, MODE>(p, stream);
 }
 
 inline int dispatch_merge(const pa_params *p, cudaStream_t stream) {

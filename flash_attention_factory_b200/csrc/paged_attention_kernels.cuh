@@ -151,12 +151,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 // the rescaling of the accumulator.
 constexpr float kRescaleThreshold = 8.0f;
 
-template <int D, int KV, int NWARPS = 4>
+template <int D, int KV, int NWARPS = 4, int TILES = 1>
 struct SmemLayout {
-  using policy = paged_attention_policy_v2<D, KV, NWARPS>;
+  using policy = paged_attention_policy_v2<D, KV, NWARPS, TILES>;
   using geo = typename policy::geometry;
   static constexpr uint32_t NW = policy::consumer_warps;
-  static constexpr uint32_t ROWS = policy::tokens_per_stage; // 64 rows: hpc heads x 64/hpc tokens
+  // rows of a stage: hpc heads x (64 * TILES / hpc) tokens, head-major
+  static constexpr uint32_t ROWS = policy::tokens_per_stage;
   static constexpr uint32_t NSTAGES = policy::ring_stages;
   static constexpr uint32_t SLAB_TILE = ROWS * geo::slab_bytes;   // one slab of one stage
   static constexpr uint32_t KV_TILE = geo::num_slabs * SLAB_TILE; // K (or V) of one stage
@@ -415,12 +416,12 @@ __device__ __noinline__ void merge_cluster_rows(float *areas, __half *out, const
   }
 }
 
-template <int D, int KV, int MODE, int NWARPS = 4>
-__global__ void __launch_bounds__(paged_attention_policy_v2<D, KV, NWARPS>::threads_per_cta,
-                                  paged_attention_policy_v2<D, KV, NWARPS>::ctas_per_sm)
+template <int D, int KV, int MODE, int NWARPS = 4, int TILES = 1>
+__global__ void __launch_bounds__(paged_attention_policy_v2<D, KV, NWARPS, TILES>::threads_per_cta,
+                                  paged_attention_policy_v2<D, KV, NWARPS, TILES>::ctas_per_sm)
 paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const AttnArgs args) {
-  using L = SmemLayout<D, KV, NWARPS>;
+  using L = SmemLayout<D, KV, NWARPS, TILES>;
   using policy = typename L::policy;
   using geo = typename L::geo;
   constexpr uint32_t NW = L::NW;
@@ -447,7 +448,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t hpc = args.hpc;
-  const uint32_t tps = args.tokens_per_stage;
+  const uint32_t tps = args.tokens_per_stage; // tokens of a KV head in one stage
+  const uint32_t tpt = tps / TILES;           // ... that the warps consume in one tile step
 #ifdef PA_TIMELINE
   const uint32_t timeline_cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
   if (threadIdx.x == 32) {
@@ -672,22 +674,24 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
   } else {
     // =========================== consumer warps ==========================
-    const uint32_t cw = warp - 1; // 0..NW-1: rows [16 cw, 16 cw + 16) of every stage
+    const uint32_t cw = warp - 1; // 0..NW-1
     const uint32_t gid = lane >> 2;
     const uint32_t t4 = lane & 3u;
     const uint32_t G = args.group;
     const uint32_t ctid = threadIdx.x - 32; // 0 .. NCONS-1
-    // warp -> (head inside the group, 16-token slice inside the stage)
+    // warp -> (head inside the group, 16-token slice inside a tile step)
     const uint32_t slices = NW / hpc; // token slices per head: 4, 2 or 1
     const uint32_t my_head = cw / slices;
     const uint32_t my_slice = cw % slices;
+    // first row of this warp's tile in tile step 0 of a stage; step k lies k * tpt rows further
+    const uint32_t warp_row = my_head * tps + my_slice * 16;
 
     // lane-dependent, stage-independent parts of the ldmatrix addresses; the chunk pair
     // 2k, 2k+1 of a slab is reached by XOR-ing (k << 5) into the address
     const uint32_t ring_base = smem_u32(smem);
-    const uint32_t lm_row_a = cw * 16 + (lane & 7u) + ((lane >> 3) & 1u) * 8u;
+    const uint32_t lm_row_a = warp_row + (lane & 7u) + ((lane >> 3) & 1u) * 8u;
     const uint32_t lm_off_a = swizzled_offset<geo::slab_bytes>(lm_row_a, lane >> 4); // K, FP8 V
-    const uint32_t lm_row_b = cw * 16 + (lane & 7u) + (lane >> 4) * 8u;
+    const uint32_t lm_row_b = warp_row + (lane & 7u) + (lane >> 4) * 8u;
     const uint32_t lm_off_b = swizzled_offset<geo::slab_bytes>(lm_row_b, (lane >> 3) & 1u); // fp16 V
     constexpr uint32_t PAIRS_PER_SLAB = geo::chunks_per_slab / 2;
 
@@ -868,39 +872,56 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       }
 
       const uint32_t my_tokens = cur.tok_end - cur.tok_begin;
-      const uint32_t my_stages = divide_round_up(my_tokens, tps);
-      // Two stages per iteration: their score tiles are independent instruction streams
-      // (more work in flight per warp) and share one softmax step.
-      for (uint32_t st = 0; st < my_stages; st += 2) {
-        const bool has_b = st + 1 < my_stages;
-        const uint32_t slot_a = slot, phase_a = phase;
-        if (++slot == NSTAGES) {
-          slot = 0;
-          phase ^= 1u;
-        }
-        const uint32_t slot_b = slot, phase_b = phase;
-        if (has_b && ++slot == NSTAGES) {
-          slot = 0;
-          phase ^= 1u;
+      const uint32_t my_steps = divide_round_up(my_tokens, tpt); // tile steps of the item
+      // Two tile steps per iteration: their score tiles are independent instruction streams
+      // (more work in flight per warp) and share one softmax step.  With one tile per stage the
+      // two steps are two stages; with 2 or 4 they lie in the same stage, TILES / 2 pairs of it.
+      for (uint32_t st = 0; st < my_steps; st += 2) {
+        const bool has_b = st + 1 < my_steps;
+        uint32_t slot_a, phase_a, slot_b, phase_b, sub_a = 0, sub_b = 0;
+        bool first_touch = true, last_touch = true; // of the stage that holds both steps (TILES > 1)
+        if constexpr (TILES == 1) {
+          slot_a = slot, phase_a = phase;
+          if (++slot == NSTAGES) {
+            slot = 0;
+            phase ^= 1u;
+          }
+          slot_b = slot, phase_b = phase;
+          if (has_b && ++slot == NSTAGES) {
+            slot = 0;
+            phase ^= 1u;
+          }
+        } else {
+          sub_a = st % TILES;
+          sub_b = sub_a + 1;
+          slot_a = slot_b = slot;
+          phase_a = phase_b = phase;
+          first_touch = sub_a == 0;
+          last_touch = sub_b + 1 == TILES || st + 2 >= my_steps;
+          if (last_touch && ++slot == NSTAGES) {
+            slot = 0;
+            phase ^= 1u;
+          }
         }
         // after an abort the loops keep their shape (the named barriers below need every
         // consumer warp) but no longer wait or compute
-        if (alive) alive = mbar_wait_bounded(&full_bar[slot_a], phase_a, abort_flag);
+        if (alive && first_touch) alive = mbar_wait_bounded(&full_bar[slot_a], phase_a, abort_flag);
 #ifdef PA_TIMELINE
         if (ctid == 0 && timeline_first) {
           PA_STAMP(3);
           timeline_first = false;
         }
 #endif
-        if (alive && has_b) alive = mbar_wait_bounded(&full_bar[slot_b], phase_b, abort_flag);
-        const uint32_t tok_a = st * tps + my_slice * 16; // first token of this warp's tile A
-        const uint32_t tok_b = tok_a + tps;
+        if (TILES == 1 && alive && has_b) alive = mbar_wait_bounded(&full_bar[slot_b], phase_b, abort_flag);
+        const uint32_t tok_a = st * tpt + my_slice * 16; // first token of this warp's tile A
+        const uint32_t tok_b = tok_a + tpt;
+        // stage bases, moved to the tile step inside the stage
+        const uint32_t base_a = ring_base + slot_a * L::STAGE_BYTES + sub_a * tpt * geo::slab_bytes;
+        const uint32_t base_b = ring_base + slot_b * L::STAGE_BYTES + sub_b * tpt * geo::slab_bytes;
         bool released_a = false;
         if (alive && has_b && !modifiers && tok_b + 16u <= my_tokens) {
           // ---- the common case, two full tiles and no score modifiers, free of branches up
           // to the rescale test; every value is computed as in the general case below
-          const uint32_t base_a = ring_base + slot_a * L::STAGE_BYTES;
-          const uint32_t base_b = ring_base + slot_b * L::STAGE_BYTES;
           float ca[4], cb[4];
           score_tile_pair(base_a + lm_off_a, base_b + lm_off_a, qf, ca, cb);
           m_true[0] = fmaxf(m_true[0], quad_column_max(fmaxf(fmaxf(ca[0], ca[2]), fmaxf(cb[0], cb[2]))) * scale);
@@ -935,18 +956,18 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           const uint32_t pb_lo = movmatrix_trans(pack_half2(pb[0], pb[1]));
           const uint32_t pb_hi = movmatrix_trans(pack_half2(pb[2], pb[3]));
           value_tile(base_a + L::KV_TILE, pa_lo, pa_hi, acc);
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&empty_bar[slot_a]); // stage A goes back before stage B is used
-          released_a = true;
+          if constexpr (TILES == 1) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[slot_a]); // stage A goes back before stage B is used
+            released_a = true;
+          }
           value_tile(base_b + L::KV_TILE, pb_lo, pb_hi, acc);
         } else if (alive && tok_a < my_tokens) {
           const bool act_b = has_b && tok_b < my_tokens;
           const uint32_t n_a = min(16u, my_tokens - tok_a);
           const uint32_t n_b = act_b ? min(16u, my_tokens - tok_b) : 0u;
-          const uint32_t base_a = ring_base + slot_a * L::STAGE_BYTES;
-          const uint32_t base_b = ring_base + slot_b * L::STAGE_BYTES;
-          if (n_a < 16u) zero_value_rows(base_a + L::KV_TILE, cw * 16 + n_a, 16u - n_a, lane);
-          if (act_b && n_b < 16u) zero_value_rows(base_b + L::KV_TILE, cw * 16 + n_b, 16u - n_b, lane);
+          if (n_a < 16u) zero_value_rows(base_a + L::KV_TILE, warp_row + n_a, 16u - n_a, lane);
+          if (act_b && n_b < 16u) zero_value_rows(base_b + L::KV_TILE, warp_row + n_b, 16u - n_b, lane);
 
           // ---- S^T = K . Q^T ; lane holds S[tok gid][g 2t4, 2t4+1] in [0],[1] and
           // S[tok gid+8][..] in [2],[3]
@@ -964,7 +985,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
             const float nat = scale * kLn2; // sm_scale * k scale
             const int32_t last = static_cast<int32_t>(cur.ctx) - 1;
             const int32_t t_a = static_cast<int32_t>(cur.tok_begin + tok_a + gid);
-            const int32_t t_b = t_a + static_cast<int32_t>(tps);
+            const int32_t t_b = t_a + static_cast<int32_t>(tpt);
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
               const int32_t row = (j >> 1) * 8; // [2],[3] belong to token gid + 8
@@ -1024,7 +1045,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
             const uint32_t p_hi = movmatrix_trans(pack_half2(pa[2], pa[3])); // tokens 8..15
             value_tile(base_a + L::KV_TILE, p_lo, p_hi, acc);
           }
-          if (has_b) {
+          if (TILES == 1 && has_b) {
             // stage A is no longer needed: hand it back before working on stage B
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[slot_a]);
@@ -1039,8 +1060,12 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         // this warp is done with the stages: let the producer refill them
         __syncwarp();
         if (alive && lane == 0) {
-          if (!released_a) mbar_arrive(&empty_bar[slot_a]);
-          if (has_b) mbar_arrive(&empty_bar[slot_b]);
+          if constexpr (TILES == 1) {
+            if (!released_a) mbar_arrive(&empty_bar[slot_a]);
+            if (has_b) mbar_arrive(&empty_bar[slot_b]);
+          } else {
+            if (last_touch) mbar_arrive(&empty_bar[slot_a]);
+          }
         }
       }
 

@@ -42,7 +42,13 @@ struct kv_tile_geometry {
 // warps and one CTA per SM with a ring twice as large.  The wide shape lets a CTA take eight KV
 // heads at once, which doubles the size of every TMA box; a warp does the same work on its
 // head in both shapes, so the results are the same bit for bit.
-template <uint32_t max_head_size_, int kv_type_, uint32_t consumer_warps_ = 4>
+//
+// stage_tiles_ is the number of 16-token tiles of a KV head that one ring stage holds per MMA
+// warp (1, 2 or 4).  KV blocks of 32 tokens and more can be fetched with one TMA box of up to
+// 16 * stage_tiles_ rows per head, so a larger stage means larger copies (the memory system
+// streams 8-16 KB copies best) where the rows are short (FP8, head size 64); the ring keeps its
+// size and holds fewer, larger stages.  The order of operations on a token does not depend on it.
+template <uint32_t max_head_size_, int kv_type_, uint32_t consumer_warps_ = 4, uint32_t stage_tiles_ = 1>
 struct paged_attention_policy_v2 : paged_attention_base_policy {
   using geometry = kv_tile_geometry<max_head_size_, kv_type_>;
   static constexpr uint32_t max_head_size = max_head_size_;
@@ -56,8 +62,11 @@ struct paged_attention_policy_v2 : paged_attention_base_policy {
   // ---- sm_100a geometry ----
   static_assert(consumer_warps_ == 4 || consumer_warps_ == 8, "4 or 8 MMA warps");
   static constexpr uint32_t consumer_warps = consumer_warps_;       // MMA warps
+  static_assert(stage_tiles_ == 1 || stage_tiles_ == 2 || stage_tiles_ == 4, "1, 2 or 4 tiles per warp and stage");
+  static constexpr uint32_t stage_tiles = stage_tiles_;
   static constexpr uint32_t tokens_per_warp = 16;                   // M extent of m16n8k16
-  static constexpr uint32_t tokens_per_stage = consumer_warps * tokens_per_warp; // 64
+  static constexpr uint32_t rows_per_tile_step = consumer_warps * tokens_per_warp; // rows all warps consume at once: 64
+  static constexpr uint32_t tokens_per_stage = rows_per_tile_step * stage_tiles_;  // rows of a stage: 64, 128 or 256
   static constexpr uint32_t threads_per_cta = (consumer_warps + 1) * 32; // + 1 TMA warp
   static constexpr uint32_t stage_bytes = 2u * tokens_per_stage * geometry::row_bytes; // K + V
   // Two CTAs per SM, each with a ring of about 96 KB (3 stages of 32 KB for fp16 / head 128,
@@ -74,6 +83,7 @@ struct paged_attention_policy_v2 : paged_attention_base_policy {
   static constexpr uint32_t ring_stages = ring_stages_raw > 8u ? 8u : ring_stages_raw;
   static_assert(ring_stages >= 2, "ring too shallow");
   static_assert(partition_size % tokens_per_stage == 0, "partition must be whole stages");
+  static_assert(ring_stages_raw >= 2, "stage too large for the ring");
 };
 
 // The loop variant uses the same knobs (reference :64-100).
