@@ -787,7 +787,9 @@ def main() -> None:
     overridden = any(v is not None for v in (a.num_seqs, a.kv, a.head_size, a.heads, a.kv_heads, a.block_size,
                                               a.block_order, a.cache_copies))
     variant = a.variant or spec["variant"]
-    shard = "none" if world == 1 else (a.shard or ("lpt" if a.config == "c5" else "replicas"))
+    scheme = a.shard or ("lpt" if a.config == "c5" else "replicas")  # how the workload divides over GPUs
+    shard = "none" if world == 1 else scheme
+    a.strong = scheme in ("lpt", "contiguous", "heads")  # total work fixed as N grows (also said at N = 1)
     seed = CONFIG_SEEDS[a.config]
 
     if a.impl == "reference":
@@ -886,13 +888,12 @@ def main() -> None:
         errors = m["errors"]
         all_ok = bool(errors["within_tol"]) and all(v.get("errors", {}).get("within_tol", True)
                                                     for v in variants.values())
-        strong = shard in ("lpt", "contiguous", "heads")
         line = {
             "metric": "decode_attention_kv_GBps", "value": round(m["gbs"], 1), "unit": "GB/s",
             "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": round(m["ms_total"] / a.steps, 5), "calls_per_step": m["calls_per_step"],
             "us_per_call": round(m["us_per_call"], 2), "higher_is_better": True,
-            "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "scaling": "strong" if a.strong else "weak", "vs_baseline": None,
             "dtype": "f16 x f16 -> f32 (mma.sync), KV stored as " + spec["kv"], "data": "synthetic",
             "config": dict(describe_config(a, spec, variant, world, ctx_all, shard),
                            calls_per_step=m["calls_per_step"], timed_region_ms=round(m["ms_total"], 1),
@@ -1061,7 +1062,7 @@ def run_reference_arm(a, spec: dict, variant: str, world: int, shard: str) -> No
     print(json.dumps({
         "impl": "reference", "metric": "decode_attention_kv_GBps", "value": round(value, 4), "unit": "GB/s",
         "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(dt * 1e3, 3),
-        "higher_is_better": True, "scaling": "strong" if shard in ("lpt", "contiguous", "heads") else "weak",
+        "higher_is_better": True, "scaling": "strong" if a.strong else "weak",
         "vs_baseline": None, "dtype": "f32 (CPU)",
         "data": "synthetic",
         "config": describe_config(a, spec, variant, world, ctx, shard),
