@@ -577,6 +577,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t chunks_per_batch = 32 / hpc;
     uint32_t slot = 0, phase = 0; // ring position, continuous across work items
     bool alive = true;
+    // lane 0: stages whose full barrier it has armed, and the phase parity of the last arming
+    uint32_t armed_stages = 0, armed_parity = 0;
 
     auto fetch_block_id = [&](const WorkItem &it, uint32_t chunk) -> uint32_t {
       const uint32_t tok = it.tok_begin + chunk * rows;
@@ -642,6 +644,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
             if (alive) {
               const uint32_t chunks_here = min(chunks_per_stage, chunks_in_batch - sb * chunks_per_stage);
               mbar_arrive_expect_tx(&full_bar[slot], chunks_here * hpc * box_bytes * 2u);
+              armed_stages |= 1u << slot;
+              armed_parity = (armed_parity & ~(1u << slot)) | (phase << slot);
             }
           }
           alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
@@ -671,6 +675,13 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       if (!next_known && alive) resolve_next();
       cur = nxt;
       ++item_no;
+    }
+    if (*abort_flag != 0u && lane == 0) {
+      // A wait gave up.  Copies already issued into the ring still complete some time and
+      // would land in shared memory that belongs to the next CTA of this SM if this one left
+      // now: wait (again with a limit) until every armed stage has received its bytes.
+      for (uint32_t s = 0; s < NSTAGES; ++s)
+        if ((armed_stages >> s) & 1u) mbar_wait_limited(&full_bar[s], (armed_parity >> s) & 1u, 20000000ull);
     }
   } else {
     // =========================== consumer warps ==========================
@@ -1300,10 +1311,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
   }
   if (threadIdx.x == 32) PA_STAMP(5);
-  if (*abort_flag != 0u) {
-    __nanosleep(200000); // give copies that are still in flight time to land
-    if (threadIdx.x == 32) atomicExch(&g_pa_device_status, 4);
-  }
+  // after a give-up the CTA's shared memory stays allocated until its last thread has left,
+  // which is the producer lane once the copies in flight have landed (see above)
+  if (*abort_flag != 0u && threadIdx.x == 32) atomicExch(&g_pa_device_status, 4);
 }
 
 // Context length as the attention kernel cut it (load_context): the merge reads exactly the

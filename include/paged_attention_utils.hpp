@@ -206,6 +206,18 @@ PA_DEV bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, volatile uint32_t 
   return true;
 }
 
+// Waits for a phase of `bar` for at most `limit_ns`, whatever the abort flag says: used after
+// a give-up to let copies that are already in flight land before the CTA leaves.
+PA_DEV bool mbar_wait_limited(uint64_t *bar, uint32_t parity, uint64_t limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 0xffu) == 0u && global_timer_ns() - t0 > limit_ns) return false;
+  }
+  return true;
+}
+
 // ------------------------------------------------------------------------ TMA
 // L2 policy for data that is read exactly once (the KV stream): evict it first
 PA_DEV uint64_t l2_evict_first_policy() {
