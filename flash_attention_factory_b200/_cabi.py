@@ -82,6 +82,8 @@ class PaParams(ctypes.Structure):
         ("reserved2", ctypes.c_float),
         ("seq_indices", ctypes.c_void_p),
         ("block_table_offsets", ctypes.c_void_p),
+        ("k_scale_per_block", ctypes.c_void_p),
+        ("v_scale_per_block", ctypes.c_void_p),
     ]
 
 

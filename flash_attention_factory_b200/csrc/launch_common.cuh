@@ -45,6 +45,25 @@ template <int D, int KV>
 int encode_cache_map(CUtensorMap *map, const void *cache, const pa_params *p, uint32_t rows_per_box,
                      uint32_t heads_per_box) {
   using geo = kv_tile_geometry<D, KV>;
+  // A decode loop calls with the same cache pointer and shape step after step: the last few
+  // descriptors of this thread are kept and reused (encoding one costs about a microsecond of
+  // host time, which a call on a tiny batch notices).
+  struct Entry {
+    const void *cache;
+    uint64_t num_blocks;
+    uint32_t block_size, num_kv_heads, rows_per_box, heads_per_box;
+    bool valid;
+    CUtensorMap map;
+  };
+  constexpr uint32_t kEntries = 8;
+  static thread_local Entry recent[kEntries] = {};
+  static thread_local uint32_t next_victim = 0;
+  for (const Entry &e : recent)
+    if (e.valid && e.cache == cache && e.num_blocks == p->num_blocks && e.block_size == p->block_size &&
+        e.num_kv_heads == p->num_kv_heads && e.rows_per_box == rows_per_box && e.heads_per_box == heads_per_box) {
+      *map = e.map;
+      return PA_OK;
+    }
   EncodeTiledFn encode = get_encode_tiled();
   if (encode == nullptr) return fail(PA_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(p->num_blocks) * p->block_size,
@@ -74,6 +93,16 @@ int encode_cache_map(CUtensorMap *map, const void *cache, const pa_params *p, ui
   const CUresult r = encode(map, dt, 3, const_cast<void *>(cache), dims, strides, box, elem_strides,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, sw, l2, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(PA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  Entry &slot = recent[next_victim];
+  next_victim = (next_victim + 1) % kEntries;
+  slot.cache = cache;
+  slot.num_blocks = p->num_blocks;
+  slot.block_size = p->block_size;
+  slot.num_kv_heads = p->num_kv_heads;
+  slot.rows_per_box = rows_per_box;
+  slot.heads_per_box = heads_per_box;
+  slot.map = *map;
+  slot.valid = true;
   return PA_OK;
 }
 
@@ -100,8 +129,13 @@ inline int validate_params(const pa_params *p, bool fp8_entry, bool needs_scratc
   }
   if (!(p->sm_scale > 0.f) || (fp8_entry && !(p->fp8_scale > 0.f)))
     return fail(PA_ERR_BAD_ARG, "sm_scale and fp8_scale must be positive and finite");
-  if (!fp8_entry && (p->k_scale_per_head != nullptr || p->v_scale_per_head != nullptr))
-    return fail(PA_ERR_BAD_ARG, "per-head scales belong to the FP8 entry points");
+  if (!fp8_entry && (p->k_scale_per_head != nullptr || p->v_scale_per_head != nullptr ||
+                     p->k_scale_per_block != nullptr || p->v_scale_per_block != nullptr))
+    return fail(PA_ERR_BAD_ARG, "per-head and per-block scales belong to the FP8 entry points");
+  if ((p->k_scale_per_block != nullptr) != (p->v_scale_per_block != nullptr))
+    return fail(PA_ERR_BAD_ARG, "k_scale_per_block and v_scale_per_block must be set together");
+  if (p->k_scale_per_block != nullptr && (p->k_scale_per_head != nullptr || p->v_scale_per_head != nullptr))
+    return fail(PA_ERR_BAD_ARG, "per-block and per-head scales exclude each other");
   if (p->num_seqs == 0) return PA_OK; // nothing to do; the launcher returns early
   if (!p->out || !p->query || !p->key_cache || !p->value_cache || !p->block_tables || !p->context_lens)
     return fail(PA_ERR_BAD_ARG, "a required pointer is null");
@@ -252,7 +286,9 @@ AttnArgs make_attn_args(const pa_params *p, uint32_t hpc) {
   a.boxes_per_stage = a.hpc * (a.tokens_per_stage / a.rows_per_box);
   // one TMA box spans all of the CTA's heads when a box fills the stage's rows of a head
   a.heads_per_box = (a.rows_per_box == a.tokens_per_stage) ? a.hpc : 1u;
-  const float kv_scale = (KV == KV_F16) ? 1.f : p->fp8_scale;
+  // with per-block scales every tile brings its own K and V scale and fp8_scale is not used
+  const bool per_block = (KV != KV_F16) && p->k_scale_per_block != nullptr;
+  const float kv_scale = (KV == KV_F16 || per_block) ? 1.f : p->fp8_scale;
   // the FP8 scale is applied once, hoisted out of the dot products
   // (reference paged_attention_kernel_fp8_loop.hpp:333,545)
   a.scale_log2 = p->sm_scale * kv_scale * kLog2e;
@@ -260,6 +296,8 @@ AttnArgs make_attn_args(const pa_params *p, uint32_t hpc) {
   a.sm_scale_log2 = p->sm_scale * kLog2e;
   a.k_scale_per_head = (KV == KV_F16) ? nullptr : p->k_scale_per_head;
   a.v_scale_per_head = (KV == KV_F16) ? nullptr : p->v_scale_per_head;
+  a.k_scale_per_block = per_block ? p->k_scale_per_block : nullptr;
+  a.v_scale_per_block = per_block ? p->v_scale_per_block : nullptr;
   a.seq_indices = p->seq_indices;
   a.alibi_slopes = p->alibi_slopes;
   a.softcap = (p->softcap > 0.f) ? p->softcap : 0.f;

@@ -123,6 +123,10 @@ struct AttnArgs {
   // set they take the place of fp8_scale for K and for V
   const float *k_scale_per_head;
   const float *v_scale_per_head;
+  // optional per-block dequantisation scales of an FP8 cache, [num_blocks, num_kv_heads] each
+  // (both or neither): the producer stages them in shared memory beside every ring stage
+  const float *k_scale_per_block;
+  const float *v_scale_per_block;
   float sm_scale_log2;       // sm_scale * log2(e)
   uint32_t sched_slot;       // row of g_sched this launch uses (split mode)
   // max_blocks_per_seq * block_size (saturated to 32 bits): a context length beyond it is cut
@@ -175,7 +179,11 @@ struct SmemLayout {
   // after the ring barriers: abort flag (16 B), then the item queue between the producer and
   // the consumers: two entries, each an item number and a full / empty mbarrier pair
   static constexpr uint32_t SCHED_OFFSET = BAR_OFFSET + 2 * NSTAGES * 8 + 16;
-  static constexpr uint32_t TOTAL_BYTES = SCHED_OFFSET + 4 * 8 + 16;
+  // per-block FP8 scales of a stage: (K scale, V scale) for each of its at most 8 (block, head)
+  // pairs -- 4 blocks of one head up to 1 block of 8 heads
+  static constexpr uint32_t SCALE_SLOTS = 8;
+  static constexpr uint32_t SCALES_OFFSET = SCHED_OFFSET + 4 * 8 + 16;
+  static constexpr uint32_t TOTAL_BYTES = SCALES_OFFSET + NSTAGES * SCALE_SLOTS * 8;
   static constexpr uint32_t DYN_SMEM = TOTAL_BYTES + 1024; // slack for 1024-byte alignment
   // loop mode: every warp parks (O[8][D], m[8], l[8]) on the (by then idle) ring for the
   // cluster-wide merge
@@ -444,6 +452,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   uint64_t *sched_empty = sched_full + 2;                                       // [2]
   volatile uint32_t *sched_item = reinterpret_cast<volatile uint32_t *>(sched_full + 4); // [2]
   constexpr uint32_t kNoItem = 0xffffffffu;
+  float2 *stage_scales = reinterpret_cast<float2 *>(smem + L::SCALES_OFFSET); // [NSTAGES][SCALE_SLOTS]
+  const bool block_scales = (KV != KV_F16) && args.k_scale_per_block != nullptr;
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
@@ -638,18 +648,29 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const int32_t y = static_cast<int32_t>((block_id << args.block_shift) + (tok & row_mask));
         const uint32_t chunks_in_batch = min(chunks_per_batch, total_chunks - chunk0);
         const uint32_t stages_in_batch = divide_round_up(chunks_in_batch, chunks_per_stage);
+        // per-block scales of this lane's (block, head): requested now, written beside the stage
+        // before it is armed; in steady state the wait for a free stage hides the latency
+        float2 lane_scales = make_float2(1.f, 1.f);
+        if (block_scales && valid) {
+          const size_t si = static_cast<size_t>(block_id) * args.num_kv_heads + cur.head_base + lane_head;
+          lane_scales = make_float2(__ldg(args.k_scale_per_block + si), __ldg(args.v_scale_per_block + si));
+        }
         for (uint32_t sb = 0; sb < stages_in_batch; ++sb) {
-          if (lane == 0) {
-            alive = mbar_wait_bounded(&empty_bar[slot], phase ^ 1u, abort_flag);
-            if (alive) {
-              const uint32_t chunks_here = min(chunks_per_stage, chunks_in_batch - sb * chunks_per_stage);
-              mbar_arrive_expect_tx(&full_bar[slot], chunks_here * hpc * box_bytes * 2u);
-              armed_stages |= 1u << slot;
-              armed_parity = (armed_parity & ~(1u << slot)) | (phase << slot);
-            }
-          }
+          if (lane == 0) alive = mbar_wait_bounded(&empty_bar[slot], phase ^ 1u, abort_flag);
           alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
           if (!alive) break;
+          if (block_scales) {
+            // the stage is free: its scale slots may be overwritten; the arming below releases them
+            if (valid && lane_chunk / chunks_per_stage == sb)
+              stage_scales[slot * L::SCALE_SLOTS + (lane_chunk % chunks_per_stage) * hpc + lane_head] = lane_scales;
+            __syncwarp();
+          }
+          if (lane == 0) {
+            const uint32_t chunks_here = min(chunks_per_stage, chunks_in_batch - sb * chunks_per_stage);
+            mbar_arrive_expect_tx(&full_bar[slot], chunks_here * hpc * box_bytes * 2u);
+            armed_stages |= 1u << slot;
+            armed_parity = (armed_parity & ~(1u << slot)) | (phase << slot);
+          }
           if (valid && lane_chunk / chunks_per_stage == sb && lane_head % args.heads_per_box == 0) {
             // rows of a stage: head-major, tokens_per_stage rows per head; a box that spans
             // several heads lands as [head][row][slab], which is this very layout
@@ -857,7 +878,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
                               : args.scale_log2;
       const float out_scale = (args.v_scale_per_head != nullptr) ? __ldg(args.v_scale_per_head + kv_head)
                                                                  : args.out_scale;
-      const bool modifiers = (args.alibi_slopes != nullptr) || (args.softcap > 0.f);
+      // score modifiers and per-block scales take the general path below; the straight-line
+      // path for pairs of full tiles is for the plain case only
+      const bool modifiers = (args.alibi_slopes != nullptr) || (args.softcap > 0.f) || block_scales;
       float slope[2] = {0.f, 0.f}; // ALiBi slopes of query columns 2*t4, 2*t4+1
       if (args.alibi_slopes != nullptr) {
 #pragma unroll
@@ -990,17 +1013,29 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
             cb[0] = cb[1] = cb[2] = cb[3] = neg_infinity();
           }
           float eff_scale = scale;
+          float v_scale_a = 1.f, v_scale_b = 1.f; // per-block V scales of the two tiles
+          float k_nat_a = scale * kLn2, k_nat_b = scale * kLn2; // sm_scale * k scale of the two tiles
+          if (block_scales) {
+            // tile A / B lie in one KV block each: the stage's slot for (that block, this head)
+            const uint32_t chunk_a = (sub_a * tpt + my_slice * 16u) / args.rows_per_box;
+            const uint32_t chunk_b = (sub_b * tpt + my_slice * 16u) / args.rows_per_box;
+            const float2 sa = stage_scales[slot_a * L::SCALE_SLOTS + chunk_a * hpc + my_head];
+            const float2 sb2 = act_b ? stage_scales[slot_b * L::SCALE_SLOTS + chunk_b * hpc + my_head] : make_float2(1.f, 1.f);
+            k_nat_a = args.sm_scale_log2 * kLn2 * sa.x;
+            k_nat_b = args.sm_scale_log2 * kLn2 * sb2.x;
+            v_scale_a = sa.y;
+            v_scale_b = sb2.y;
+          }
           if (modifiers) {
-            // soft-cap / ALiBi: turn the raw dot products into log2-domain logits here; the
-            // softmax below then runs with a unit scale
-            const float nat = scale * kLn2; // sm_scale * k scale
+            // soft-cap / ALiBi / per-block scales: turn the raw dot products into log2-domain
+            // logits here; the softmax below then runs with a unit scale
             const int32_t last = static_cast<int32_t>(cur.ctx) - 1;
             const int32_t t_a = static_cast<int32_t>(cur.tok_begin + tok_a + gid);
             const int32_t t_b = t_a + static_cast<int32_t>(tpt);
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
               const int32_t row = (j >> 1) * 8; // [2],[3] belong to token gid + 8
-              float xa = ca[j] * nat, xb = cb[j] * nat;
+              float xa = ca[j] * k_nat_a, xb = cb[j] * k_nat_b;
               if (args.softcap > 0.f) {
                 xa = args.softcap * tanhf(xa / args.softcap);
                 xb = args.softcap * tanhf(xb / args.softcap);
@@ -1049,6 +1084,14 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           }
           l_run[0] += (pa[0] + pa[2]) + (pb[0] + pb[2]); // fp32 sum of the unrounded weights
           l_run[1] += (pa[1] + pa[3]) + (pb[1] + pb[3]);
+          if (block_scales) {
+            // V of a block dequantises as code * scale: fold the scale into the weights
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+              pa[j] *= v_scale_a;
+              pb[j] *= v_scale_b;
+            }
+          }
           // P rounded to fp16 for the MMA, transposed into the B-operand layout;
           // ---- O^T += V^T . P^T
           {

@@ -35,7 +35,8 @@ def build_params(max_logits, exp_sums, tem_output, output, debug_output, query, 
                  value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
                  fp8_scale, block_size, max_context_len, alibi_slopes, sinks, softcap,
                  fp8: bool, k_scale_per_head=None, v_scale_per_head=None,
-                 use_alibi: bool = False, use_softcap: bool = False) -> _cabi.PaParams:
+                 use_alibi: bool = False, use_softcap: bool = False,
+                 k_scale_per_block=None, v_scale_per_block=None) -> _cabi.PaParams:
     """Validates what the reference's ``data_ptr<float>()`` calls would and fills pa_params.
 
     ``debug_output``, ``alibi_slopes``, ``softcap`` are accepted and ignored like in the
@@ -98,6 +99,13 @@ def build_params(max_logits, exp_sums, tem_output, output, debug_output, query, 
             _require(fp8, "per-head scales belong to the FP8 operators")
             _require(t.dtype == torch.float32 and t.is_contiguous() and t.device == query.device
                      and t.numel() == key_cache.size(2), f"{name} must be float32 [num_kv_heads] on the device")
+            setattr(p, name, t.data_ptr())
+    for name, t in (("k_scale_per_block", k_scale_per_block), ("v_scale_per_block", v_scale_per_block)):
+        if t is not None:
+            _require(fp8, "per-block scales belong to the FP8 operators")
+            _require(t.dtype == torch.float32 and t.is_contiguous() and t.device == query.device
+                     and tuple(t.shape) == (key_cache.size(0), key_cache.size(2)),
+                     f"{name} must be float32 [num_blocks, num_kv_heads] on the device")
             setattr(p, name, t.data_ptr())
     # opt-in only: by default alibi_slopes and softcap are ignored, as in the reference
     if use_alibi:

@@ -26,27 +26,31 @@ def run(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache
 def params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
            block_tables, context_lens, num_queries_per_tokens, sm_scale, fp8_scale, block_size,
            max_context_len, alibi_slopes, sinks, softcap, *, k_scale_per_head=None, v_scale_per_head=None,
-           use_alibi=False, use_softcap=False):
+           use_alibi=False, use_softcap=False, k_scale_per_block=None, v_scale_per_block=None):
     """The checked argument block (`pa_params`) of an ``enqueue`` call with these arguments,
     for callers that launch many steps on the same tensors (`host_io.DecodeStepIO.bind`)."""
     p = _shim.build_params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache,
                            value_cache, block_tables, context_lens, num_queries_per_tokens, sm_scale,
                            fp8_scale, block_size, max_context_len, alibi_slopes, sinks, softcap,
                            fp8=True, k_scale_per_head=k_scale_per_head, v_scale_per_head=v_scale_per_head,
-                           use_alibi=use_alibi, use_softcap=use_softcap)
+                           use_alibi=use_alibi, use_softcap=use_softcap, k_scale_per_block=k_scale_per_block,
+                           v_scale_per_block=v_scale_per_block)
     return p
 
 
 def enqueue(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
             block_tables, context_lens, num_queries_per_tokens, sm_scale, fp8_scale, block_size,
             max_context_len, alibi_slopes, sinks, softcap, *, k_scale_per_head=None, v_scale_per_head=None,
-            use_alibi=False, use_softcap=False):
+            use_alibi=False, use_softcap=False, k_scale_per_block=None, v_scale_per_block=None):
     """Same arguments as ``run`` but asynchronous on the current stream (returns nothing).
 
     ``k_scale_per_head`` / ``v_scale_per_head`` (float32 [num_kv_heads], optional, no reference
-    counterpart) replace the scalar ``fp8_scale`` for K / V with one scale per KV head."""
+    counterpart) replace the scalar ``fp8_scale`` for K / V with one scale per KV head;
+    ``k_scale_per_block`` / ``v_scale_per_block`` (float32 [num_blocks, num_kv_heads]) with one per
+    block and head."""
     p = params(max_logits, exp_sums, tem_output, output, debug_output, query, key_cache, value_cache,
                block_tables, context_lens, num_queries_per_tokens, sm_scale, fp8_scale, block_size,
                max_context_len, alibi_slopes, sinks, softcap, k_scale_per_head=k_scale_per_head,
-               v_scale_per_head=v_scale_per_head, use_alibi=use_alibi, use_softcap=use_softcap)
+               v_scale_per_head=v_scale_per_head, use_alibi=use_alibi, use_softcap=use_softcap,
+               k_scale_per_block=k_scale_per_block, v_scale_per_block=v_scale_per_block)
     _shim.enqueue_entry(_ENTRY, p, query.device)

@@ -121,6 +121,13 @@ typedef struct pa_params {
    * the sum of ceil(ctx / block_size), which is what a host uploads per step.  A context
    * length beyond what its row holds is cut to it.  NULL = dense tables. */
   const uint32_t *block_table_offsets;
+  /* Optional per-block dequantisation scales of an FP8 cache (no reference counterpart; the
+   * reference has one scalar, paged_attention_fp8_loop/paged_attention_fp8_loop.cpp:34): device
+   * arrays fp32 [num_blocks, num_kv_heads], both or neither.  K of block b, head k dequantises as
+   * fp16(code) * k_scale_per_block[b * num_kv_heads + k], V likewise; fp8_scale is then not
+   * used and the per-head scales must be NULL. */
+  const float *k_scale_per_block;
+  const float *v_scale_per_block;
 } pa_params;
 
 /* Tiling knobs of include/paged_attention_policy_v2.hpp for one

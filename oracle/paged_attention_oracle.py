@@ -99,10 +99,15 @@ def paged_attention_ref(query: torch.Tensor, key_cache: torch.Tensor, value_cach
                         sm_scale: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
                         fp8_scale: float = 1.0, k_scales: Optional[torch.Tensor] = None,
                         v_scales: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                        alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        alibi_slopes: Optional[torch.Tensor] = None,
+                        k_block_scales: Optional[torch.Tensor] = None,
+                        v_block_scales: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Reference result of all four entry points: fp16 [num_seqs, num_heads, head_size].
 
-    `k_scales` / `v_scales` ([kv_heads] each) replace `fp8_scale` for K / V when given.
+    `k_scales` / `v_scales` ([kv_heads] each) replace `fp8_scale` for K / V when given;
+    `k_block_scales` / `v_block_scales` ([num_blocks, kv_heads] each, an extension over the
+    reference's scalar) give every (block, head) its own scale: the dequantised cache is
+    fp16(code) * scale[block, head].
 
     query fp16 [S, H, D]; caches [num_blocks, block_size, HK, D] in fp16, float8_e5m2,
     float8_e4m3fn or uint8 (= e5m2).  One sequence at a time, which bounds memory the way
@@ -111,11 +116,20 @@ def paged_attention_ref(query: torch.Tensor, key_cache: torch.Tensor, value_cach
     s, h, d = query.shape
     out = torch.zeros(s, h, d, dtype=torch.float16)
     lens = [int(c) for c in context_lens]
+
+    def tokens_of(cache, block_scales, head_scales, i):
+        x = dequantize_cache(gather_sequence(cache, block_tables[i], lens[i]),
+                             1.0 if block_scales is not None else (fp8_scale if head_scales is None else head_scales))
+        if block_scales is not None:
+            bs = cache.shape[1]
+            ids = block_tables[i, :(lens[i] + bs - 1) // bs].to(torch.long)
+            per_token = block_scales.to(torch.float32)[ids].repeat_interleave(bs, dim=0)[:lens[i]]  # [ctx, kv_heads]
+            x = x * per_token.unsqueeze(-1)
+        return x
+
     for i in range(s):
-        k = dequantize_cache(gather_sequence(key_cache, block_tables[i], lens[i]),
-                             fp8_scale if k_scales is None else k_scales)
-        v = dequantize_cache(gather_sequence(value_cache, block_tables[i], lens[i]),
-                             fp8_scale if v_scales is None else v_scales)
+        k = tokens_of(key_cache, k_block_scales, k_scales, i)
+        v = tokens_of(value_cache, v_block_scales, v_scales, i)
         o = attention_one_sequence(query[i].to(torch.float32), k, v, sinks, sm_scale, softcap, alibi_slopes)
         out[i] = o.to(torch.float16)  # test_paged.py:168
     return out

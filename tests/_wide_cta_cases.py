@@ -27,6 +27,7 @@ CASES = {
     "e5m2_d128_b32_scales": ("float8_e5m2", 128, 32, 16, 8, [800, 1600, 90], True, ("scales",)),
     "e4m3_d128_b16_modifiers": ("float8_e4m3fn", 128, 16, 16, 8, [777, 40, 1300], True, ("alibi", "softcap")),
     "e5m2_d128_b16_subset": ("float8_e5m2", 128, 16, 16, 8, [600, 50, 1100, 2000, 513], False, ("subset",)),
+    "e4m3_d128_b16_block_scales": ("float8_e4m3fn", 128, 16, 16, 8, [900, 33, 1600], True, ("block_scales",)),
 }
 SUBSET = [3, 0, 4]  # sequence ids of the "subset" case, in launch order
 
@@ -41,6 +42,9 @@ def build(name):
     c["alibi"] = torch.linspace(0.01, 0.2, h) if "alibi" in extras else None
     c["softcap"] = 6.0 if "softcap" in extras else 0.0
     c["subset"] = SUBSET if "subset" in extras else None
+    nb = c["key_cache"].size(0)
+    c["k_block_scales"] = torch.rand(nb, hk, generator=g) + 0.5 if "block_scales" in extras else None
+    c["v_block_scales"] = torch.rand(nb, hk, generator=g) * 2 + 0.25 if "block_scales" in extras else None
     return c
 
 
@@ -64,10 +68,12 @@ def run_case(name, dev):
     sinks = c["sinks"].to(dev) if c["sinks"] is not None else None
     ks = c["k_scales"].to(dev) if c["k_scales"] is not None else None
     vs = c["v_scales"].to(dev) if c["v_scales"] is not None else None
+    kb = c["k_block_scales"].to(dev) if c["k_block_scales"] is not None else None
+    vb = c["v_block_scales"].to(dev) if c["v_block_scales"] is not None else None
     p = mod.params(ml, es, tmp, out, torch.zeros(1, device=dev), q, k, v, bt, cl, h // k.size(2), c["sm_scale"],
                    c["fp8_scale"], k.size(1), int(c["context_lens"].max()), alibi, sinks, c["softcap"] or -1.0,
                    k_scale_per_head=ks, v_scale_per_head=vs, use_alibi=c["alibi"] is not None,
-                   use_softcap=c["softcap"] > 0)
+                   use_softcap=c["softcap"] > 0, k_scale_per_block=kb, v_scale_per_block=vb)
     keep = None
     if c["subset"] is not None:
         keep = torch.tensor(c["subset"], dtype=torch.int32, device=dev)

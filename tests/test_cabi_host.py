@@ -75,7 +75,7 @@ def test_public_header_is_plain_c(tmp_path):
 
 def test_params_struct_matches_header_layout():
     # 10 pointers, 10 uint32, uint64, 2 floats, 2 int32 with natural alignment
-    assert ctypes.sizeof(_cabi.PaParams) == 10 * 8 + 10 * 4 + 8 + 2 * 4 + 2 * 4 + 2 * 8 + 8 + 2 * 4 + 8 + 8
+    assert ctypes.sizeof(_cabi.PaParams) == 10 * 8 + 10 * 4 + 8 + 2 * 4 + 2 * 4 + 2 * 8 + 8 + 2 * 4 + 8 + 8 + 2 * 8
     assert _cabi.PaParams.num_blocks.offset == 120
     assert _cabi.PaParams.sm_scale.offset == 128
 

@@ -36,10 +36,12 @@ def test_wide_cta_gives_the_default_shapes_bits_and_the_oracles_answer(cuda_devi
         want = oracle.paged_attention_ref(
             c["query"], c["key_cache"], c["value_cache"], c["block_tables"], c["context_lens"],
             sm_scale=c["sm_scale"], sinks=c["sinks"], fp8_scale=c["fp8_scale"], k_scales=c["k_scales"],
-            v_scales=c["v_scales"], softcap=c["softcap"], alibi_slopes=c["alibi"])
+            v_scales=c["v_scales"], softcap=c["softcap"], alibi_slopes=c["alibi"],
+            k_block_scales=c["k_block_scales"], v_block_scales=c["v_block_scales"])
         got = wide[name]
         if c["subset"] is not None:
             rest = [i for i in range(got.size(0)) if i not in c["subset"]]
             assert (got[rest] == -7.0).all(), "sequences outside the subset were written"
             got, want = got[c["subset"]], want[c["subset"]]
-        assert_close(got, want, atol=3e-3 if c["v_scales"] is not None else 1e-3, what=name)
+        scaled = c["v_scales"] is not None or c["v_block_scales"] is not None
+        assert_close(got, want, atol=3e-3 if scaled else 1e-3, what=name)
