@@ -938,10 +938,18 @@ def main() -> None:
 # under profiles/ (traffic grows in proportion to the KV bytes: every sequence streams its own
 # KV once); None until a capture exists for the workload
 TRAFFIC_RATIO: dict = {
-    # profiles/paged_attention_kernel_split_fp16_c2_small.md: (1073.96 + 3.82) MB for 1073.74 MB
-    ("c2", "reduce"): 1.00376,
-    # profiles/paged_attention_kernel_split_e4m3_c4_small.md: (537.13 + 5.65) MB for 536.87 MB
-    ("c4", "reduce"): 1.01101,
+    # profiles/paged_attention_kernel_split_e5m2_c5_small.md: (1046.30 + 7.10) MB for 1042.26 MB
+    ("c5", "reduce"): 1.01072, ("c5", "auto"): 1.01072,
+    # profiles/paged_attention_kernel_split_e4m3_c4_small.md: (537.14 + 5.04) MB for 536.87 MB
+    ("c4", "reduce"): 1.00990,
+    # profiles/paged_attention_kernel_loop_e4m3_c4_small.md: (537.14 + 3.48) MB for 536.87 MB
+    ("c4", "loop"): 1.00698,
+    # profiles/paged_attention_kernel_loop_e5m2_c3_small.md: (514.74 + 3.11) MB for 513.46 MB
+    ("c3", "loop"): 1.00854,
+    # profiles/paged_attention_kernel_fp16_c2_small.md: split (1073.97 + 3.24) MB, loop (1074.05 + 3.51) MB for 1073.74 MB
+    ("c2", "reduce"): 1.00323, ("c2", "loop"): 1.00355,
+    # profiles/paged_attention_kernel_loop_e5m2_refperf8.md: (101.10 + 2.96) MB for 98.30 MB (block tails)
+    ("refperf8", "loop"): 1.05852,
 }
 
 
