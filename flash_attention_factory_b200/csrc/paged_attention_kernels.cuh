@@ -14,17 +14,19 @@
 // (reference paged_attention_reduce, paged_attention_kernel_v2.hpp:594-970).
 //
 // Structure of the attention kernel: warp 0 walks the block table and issues
-// tiled TMA copies (one box per KV block and 128-byte slab, spanning the CTA's KV heads
-// where a block fills the stage) into a
-// ring of shared-memory stages guarded by full/empty mbarriers; warps 1..4
-// each own 16 rows of every stage.  A CTA works on `hpc` (1, 2 or 4)
-// neighbouring KV heads at once: with hpc = 4 a warp owns one KV head and sees
-// every token of the item, so nothing has to be merged across warps; with
-// fewer heads the warps split the tokens and merge through shared memory in a
-// fixed order.  A second shape of the same kernel (NWARPS = 8: warps 1..8, hpc = 8,
-// one CTA per SM, a ring twice as large) serves FP8 caches in split mode; a warp
-// does the same work on its head in both shapes, so they give the same bits.  The GQA query group sits on the N=8 extent of mma.m16n8k16 and
-// the tokens on M, so a KV byte is read from HBM once for the whole group:
+// tiled TMA copies (one box per KV block and 128-byte slab, spanning the CTA's KV
+// heads where a block fills the stage) into a ring of shared-memory stages guarded
+// by full/empty mbarriers; warps 1..4 each own a 16-row tile of every tile step of
+// a stage (TILES = 1, 2 or 4 steps per stage: larger stages mean larger copies for
+// KV blocks of 32 tokens and more).  A CTA works on `hpc` (1, 2 or 4) neighbouring
+// KV heads at once: with hpc = 4 a warp owns one KV head and sees every token of
+// the item, so nothing has to be merged across warps; with fewer heads the warps
+// split the tokens and merge through shared memory in a fixed order.  A second
+// shape of the same kernel (NWARPS = 8: warps 1..8, hpc = 8, one CTA per SM, a ring
+// twice as large) serves FP8 caches in split mode; a warp does the same work on
+// its head in both shapes, so they give the same bits.  The GQA query group sits
+// on the N=8 extent of mma.m16n8k16 and the tokens on M, so a KV byte is read from
+// HBM once for the whole group:
 //   S^T[tok, g] = K[tok, d] . Q^T[d, g]          (A = K via ldmatrix)
 //   O^T[d, g]  += V^T[d, tok] . P^T[tok, g]      (A = V via ldmatrix.trans)
 // Softmax is online per warp in the log2 domain with warp-shuffle column
@@ -229,9 +231,9 @@ __device__ __forceinline__ uint32_t load_context(const AttnArgs &args, uint32_t 
 // Split mode: the work items are the (sequence, partition, head group) triples whose partition
 // starts inside the context, numbered densely with the head group fastest (CTAs that run
 // together stream neighbouring rows of the same KV blocks) and the sequence slowest; CTA b
-// takes the items b, b + gridDim.x, ...  Partitions past a context have no number, so their
-// scratch rows stay untouched (reference paged_attention_kernel_v2.hpp:194-200,577-579) and
-// ragged batches spread evenly: every CTA gets the same count of items to within one.
+// starts with item b and draws every further number from the launch's counter.  Partitions
+// past a context have no number, so their scratch rows stay untouched (reference
+// paged_attention_kernel_v2.hpp:194-200,577-579) and ragged batches spread evenly.
 //
 // The numbering needs the running sum of items per sequence.  A warp keeps a window of 32
 // sequences in registers (one per lane) and moves it forward as its item numbers grow, so the
