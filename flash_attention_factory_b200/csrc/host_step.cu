@@ -204,6 +204,7 @@ PA_API int pa_decode_step_host_batch(int32_t entry, const pa_params *p, const pa
   PA_CUDA_TRY(cudaStreamWaitEvent(r->copy_in, r->start, 0));
   const bool direct_last = (io->flags & PA_STEP_LAST_OUT_DIRECT) != 0u;
   bool any_copy_out = false;
+  uint32_t next_offset = 0; // packed tables: first row offset that has not gone up yet
   for (uint32_t k = 0; k < n; ++k) {
     const uint32_t lo = bound[k], hi = bound[k + 1];
     if (hi <= lo) continue;
@@ -216,9 +217,10 @@ PA_API int pa_decode_step_host_batch(int32_t entry, const pa_params *p, const pa
                                 cnt * sizeof(uint32_t), cudaMemcpyHostToDevice, r->copy_in));
     if (packed) {
       const uint32_t *off = io->host_block_table_offsets;
-      const uint32_t first_off = (k == 0) ? lo : lo + 1; // offsets[lo] went up with the previous sub-batch
-      PA_CUDA_TRY(cudaMemcpyAsync(const_cast<uint32_t *>(p->block_table_offsets) + first_off, off + first_off,
-                                  (hi + 1 - first_off) * sizeof(uint32_t), cudaMemcpyHostToDevice, r->copy_in));
+      // offsets [lo, hi]; offsets[lo] has gone up with the previous sub-batch unless this is the first
+      PA_CUDA_TRY(cudaMemcpyAsync(const_cast<uint32_t *>(p->block_table_offsets) + next_offset, off + next_offset,
+                                  (hi + 1 - next_offset) * sizeof(uint32_t), cudaMemcpyHostToDevice, r->copy_in));
+      next_offset = hi + 1;
       if (off[hi] > off[lo])
         PA_CUDA_TRY(cudaMemcpyAsync(const_cast<uint32_t *>(p->block_tables) + off[lo], io->host_block_tables + off[lo],
                                     static_cast<size_t>(off[hi] - off[lo]) * sizeof(uint32_t), cudaMemcpyHostToDevice,
