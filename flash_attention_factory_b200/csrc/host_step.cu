@@ -71,7 +71,7 @@ size_t table_entries_of(const pa_params *p, const pa_host_batch *io) {
 // and tail of one more launch pair, more copies and events); cutting into n hides (1 - 1/n) of
 // the transfer time, about 16 us of latencies plus the bytes at the 25 GB/s per direction
 // measured for pinned memory on B200 hosts.  The sum is smallest near
-// n = sqrt(transfer time / 40 us).
+// n = sqrt(transfer time / 40 us) (measured: 4 for 17 MB per step, 3 for 2 MB, 1 below 1 MB).
 uint32_t choose_sub_batches(const pa_params *p, const pa_host_batch *io) {
   const uint32_t S = p->num_seqs;
   uint32_t n = io->sub_batches;
@@ -80,6 +80,7 @@ uint32_t choose_sub_batches(const pa_params *p, const pa_host_batch *io) {
     const double bytes = 2.0 * row_bytes * S + 4.0 * (static_cast<double>(table_entries_of(p, io)) + 2.0 * S);
     const double transfer_us = 16.0 + bytes / 25.0e3;
     n = static_cast<uint32_t>(std::sqrt(transfer_us / 40.0) + 0.5);
+    if (n == 2) n = 3; // from three pieces on the two end pieces are small (see the boundaries below)
   }
   return std::max(1u, std::min(std::min(n, kMaxSubBatches), std::max(S, 1u)));
 }
@@ -193,9 +194,32 @@ PA_API int pa_decode_step_host_batch(int32_t entry, const pa_params *p, const pa
   const size_t table_entries = table_entries_of(p, io);
   const uint32_t n = choose_sub_batches(p, io);
   if (n == 1) return single_batch_step(entry, p, io, packed, row_bytes, table_entries, stream, synchronize);
-  // ---- boundaries: equal shares of the batch's KV tokens (the kernels' time follows the tokens)
+  // ---- boundaries by KV tokens (the kernels' time follows the tokens).  The upload of the first
+  // sub-batch and the download of the last are the only transfers nothing hides, so the two end
+  // pieces are a third of the size of the inner ones (weights 1, 3, ..., 3, 1).
   uint32_t bound[kMaxSubBatches + 1];
-  if (int rc = pa_split_by_kv_length(io->host_context_lens, S, n, bound)) return rc;
+  {
+#ifdef PA_STEP_EQUAL_SHARES
+    const uint32_t inner = 1;
+#else
+    const uint32_t inner = (n >= 3) ? 3u : 1u;
+#endif
+    const uint64_t weight_sum = 2ull + static_cast<uint64_t>(inner) * (n - 2u);
+    uint64_t total = 0;
+    for (uint32_t i = 0; i < S; ++i) total += io->host_context_lens[i];
+    // piece r ends behind the sequence whose cumulative length reaches its cumulative weight
+    uint64_t cum = 0, weight_done = 1; // cumulative weight up to and including piece r
+    uint32_t rr = 0;
+    bound[0] = 0;
+    for (uint32_t i = 0; i < S; ++i) {
+      cum += io->host_context_lens[i];
+      while (rr + 1 < n && total > 0 && cum * weight_sum >= weight_done * total) {
+        bound[++rr] = i + 1;
+        weight_done += (rr + 1 < n) ? inner : 1u;
+      }
+    }
+    while (rr < n) bound[++rr] = S;
+  }
   StepResources *r = nullptr;
   if (int rc = step_resources(&r)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

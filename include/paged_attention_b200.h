@@ -269,7 +269,8 @@ typedef struct pa_host_batch {
 #define PA_STEP_LAST_OUT_DIRECT 1u
 
 /* One decode step with host buffers, pipelined (no counterpart in the reference).  The batch is
- * cut into sub-batches of consecutive sequences holding equal shares of the KV tokens; the
+ * cut into sub-batches of consecutive sequences by KV tokens (the first and the last a third of
+ * the size of the inner ones: their upload and download are the transfers nothing hides); the
  * upload of sub-batch k+1 (its rows of query, context lengths and block tables -- only the
  * entries in use when the tables are packed, see pa_params.block_table_offsets), the kernels of
  * sub-batch k and the download of sub-batch k-1 run at the same time, on two copy streams the
