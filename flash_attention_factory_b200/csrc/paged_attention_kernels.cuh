@@ -1389,7 +1389,7 @@ struct MergeShape {
 };
 
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 8) // 64 registers: 1 184 CTAs resident, config 4's 1 024 pairs in one wave
 merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp_out,
                         const float *__restrict__ max_logits, const float *__restrict__ exp_sums,
                         const uint32_t *__restrict__ context_lens, const uint32_t *__restrict__ seq_indices,
@@ -1406,8 +1406,6 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
   // kernel drains; nothing is read before that kernel has completed and its writes are visible.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const uint32_t ctx = merge_context(context_lens, seq, ctx_limit, table_offsets, block_shift);
-  const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
   const size_t base = (static_cast<size_t>(seq) * num_heads + head) * max_num_partitions;
   __half *orow = out + (static_cast<size_t>(seq) * num_heads + head) * D;
 
@@ -1417,18 +1415,28 @@ merge_partitions_kernel(__half *__restrict__ out, const __half *__restrict__ tmp
 
   const uint32_t row = tid / LANES_PER_ROW;
   const uint32_t col = (tid % LANES_PER_ROW) * 4;
-  // first UNROLL rows of this thread: requested now, used after the weights are ready
+  // The first UNROLL rows of this thread and the first 128 partitions' statistics are requested
+  // together with the context length, for every partition the scratch has room for: rows past
+  // the context hold whatever the caller left there and are masked once the length is known.
+  // One memory round trip instead of two.
   uint2 raw[UNROLL];
 #pragma unroll
   for (uint32_t u = 0; u < UNROLL; ++u) {
     const uint32_t p = row + u * ROWS;
-    raw[u] = (p < np) ? __ldg(reinterpret_cast<const uint2 *>(tmp_out + (base + p) * D + col)) : make_uint2(0u, 0u);
+    raw[u] = (p < max_num_partitions) ? __ldg(reinterpret_cast<const uint2 *>(tmp_out + (base + p) * D + col))
+                                      : make_uint2(0u, 0u);
+  }
+  float ml_own = (tid < max_num_partitions) ? max_logits[base + tid] : neg_infinity();
+  float es_own = (tid < max_num_partitions) ? exp_sums[base + tid] : 0.f;
+  const uint32_t ctx = merge_context(context_lens, seq, ctx_limit, table_offsets, block_shift);
+  const uint32_t np = min(num_partitions_of(ctx, partition_size), max_num_partitions);
+  if (tid >= np) {
+    ml_own = neg_infinity();
+    es_own = 0.f;
   }
 
   // global max over partitions; the first 128 partitions' statistics stay in registers, so
   // the weights below need no second trip to memory
-  const float ml_own = (tid < np) ? max_logits[base + tid] : neg_infinity();
-  const float es_own = (tid < np) ? exp_sums[base + tid] : 0.f;
   float m = ml_own;
   for (uint32_t p = tid + 128; p < np; p += 128) m = fmaxf(m, max_logits[base + p]);
 #pragma unroll
