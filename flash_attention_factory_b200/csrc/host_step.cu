@@ -199,11 +199,7 @@ PA_API int pa_decode_step_host_batch(int32_t entry, const pa_params *p, const pa
   // pieces are a third of the size of the inner ones (weights 1, 3, ..., 3, 1).
   uint32_t bound[kMaxSubBatches + 1];
   {
-#ifdef PA_STEP_EQUAL_SHARES
-    const uint32_t inner = 1;
-#else
     const uint32_t inner = (n >= 3) ? 3u : 1u;
-#endif
     const uint64_t weight_sum = 2ull + static_cast<uint64_t>(inner) * (n - 2u);
     uint64_t total = 0;
     for (uint32_t i = 0; i < S; ++i) total += io->host_context_lens[i];

@@ -388,7 +388,7 @@ int enqueue_merge(const pa_params *p, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  // Many (sequence, head) pairs: a warp per pair keeps more rows in flight than a CTA per pair.
+  // Many (sequence, head) pairs: a warp per pair runs them in fewer waves than a CTA per pair.
   // Both kernels add in the same order and give the same bits (tested), so the choice is free.
   // Debugging knob: PA_MERGE_KERNEL=cta|warp forces one of them.
   static const int forced = [] {
@@ -396,7 +396,14 @@ int enqueue_merge(const pa_params *p, cudaStream_t stream) {
     return e == nullptr ? 0 : (e[0] == 'c' ? 1 : (e[0] == 'w' ? 2 : 0));
   }();
   const uint64_t pairs = static_cast<uint64_t>(p->num_seqs) * p->num_heads;
-  if (forced == 2 || (forced == 0 && pairs >= 8192)) {
+  // Measured on B200: from 2048 pairs on the warps win (4096 pairs of up to 6 partitions: 39.0
+  // against 43.9 us per call; 2048 pairs of 8: 601 against 604); 1024 pairs of 64 partitions are
+  // faster with a CTA each (174 against 181), whose threads fetch all 64 rows at once, so long
+  // contexts need twice the pairs.
+  uint32_t parts = p->max_num_partitions;
+  if (context_hint(p) != 0u) parts = std::min(parts, divide_round_up(context_hint(p), psize));
+  const bool many_pairs = pairs >= (parts > 32u ? 4096u : 2048u);
+  if (forced == 2 || (forced == 0 && many_pairs)) {
     cfg.gridDim = dim3(static_cast<unsigned>((pairs + 3) / 4), 1, 1);
     PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partitions_warp_kernel<D>, static_cast<__half *>(p->out),
                                    static_cast<const __half *>(p->tmp_out),
