@@ -318,8 +318,10 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream, uint32_t hpc) {
   AttnArgs args = make_attn_args<D, KV, NWARPS, TILES>(p, hpc);
   if (MODE == MODE_SPLIT) {
     // one allocator per translation unit, like the counter table it indexes
+    // (the legacy default stream cannot be captured, and asking about it while another stream
+    // captures in global mode would invalidate that capture)
     cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
-    PA_CUDA_TRY(cudaStreamIsCapturing(stream, &capture));
+    if (stream != nullptr && stream != cudaStreamLegacy) PA_CUDA_TRY(cudaStreamIsCapturing(stream, &capture));
     args.sched_slot = next_sched_slot(capture != cudaStreamCaptureStatusNone);
   }
   CUtensorMap map_k, map_v;
