@@ -14,8 +14,9 @@
  * by the caller and lives on the current CUDA device; the library allocates
  * nothing on the device.  The only state it keeps between calls is a table of
  * work counters inside its device image, of which every split-context launch
- * takes a row of its own and hands it back zeroed (see INTEGRATION.md on
- * overlapping launches and CUDA graphs).
+ * takes a row of its own and hands it back zeroed: calls on different streams
+ * (with different scratch buffers) may overlap, and a launch recorded into a
+ * CUDA graph keeps its row for every replay, in a range direct launches never use.
  *
  * Data layouts (reference paged_attention_kernel_loop.hpp:44-62):
  *   query        fp16  [num_seqs, num_heads, head_size]

@@ -1,6 +1,6 @@
 """Split-context launches of different kernel instantiations that run at the same time.
 
-INTEGRATION.md allows calls on different streams (with different buffers) to overlap.  The
+The library's contract allows calls on different streams (with different buffers) to overlap.  The
 split kernel draws its work items from a table of counters of which every launch must hold a
 row of its own; the table is shared by all instantiations of a translation unit (wide and
 default CTA shape, e5m2 and e4m3, head 128 and 64).  A child process (fresh counter state,
