@@ -540,7 +540,7 @@ def check_errors(w: Workload, max_seqs: int = 6, e2e=None) -> dict:
 
 
 def measure_workload(w: Workload, a, group: Group, min_seconds: float, e2e_seconds: float, with_errors: bool,
-                     kernel_reps: int = 20, graph: bool = False, error_seqs: int = 6) -> dict:
+                     kernel_reps: int = 20, graph: bool = False, error_seqs: int = 6, sampler=None) -> dict:
     """Times one workload on this rank (and, through `group`, on all ranks): device-resident
     calls, the attention kernel alone, and the host-buffer step."""
     graphs = None
@@ -601,6 +601,7 @@ def measure_workload(w: Workload, a, group: Group, min_seconds: float, e2e_secon
             w.out = resident_out
 
     ms_e2e, cps_e2e = timed_calls(e2e_call, a.steps, 3, e2e_seconds, group)
+    clocks = sampler.stop() if sampler is not None else None  # the clock record covers the timed regions only
     errors = check_errors(w, max_seqs=error_seqs, e2e=e2e) if with_errors else None
     calls, calls_e2e = a.steps * cps, a.steps * cps_e2e
     kernel = statistics.mean(attn_us) if attn_us else ms_total / calls * 1e3
@@ -612,7 +613,7 @@ def measure_workload(w: Workload, a, group: Group, min_seconds: float, e2e_secon
         "kernel_us": kernel, "kernel_gbs": w.kv_bytes / (kernel * 1e-6) / 1e9,
         "merge_us": statistics.mean(merge_us) if merge_us else None,
         "e2e_us_per_call": ms_e2e / calls_e2e * 1e3, "e2e_gbs": job_bytes / (ms_e2e / calls_e2e * 1e-3) / 1e9,
-        "e2e_calls_per_step": cps_e2e, "e2e_plan": plan, "errors": errors,
+        "e2e_calls_per_step": cps_e2e, "e2e_plan": plan, "errors": errors, "clocks": clocks,
         "launches": calls * w.launches_per_step,
     }
 
@@ -822,8 +823,8 @@ def main() -> None:
     if rank == 0:
         sampler.start()
     m = measure_workload(w, a, group, a.min_seconds, max(0.3, a.min_seconds / 2), with_errors=True,
-                         graph=a.cuda_graph)
-    clocks = sampler.stop() if rank == 0 else None
+                         graph=a.cuda_graph, sampler=sampler if rank == 0 else None)
+    clocks = m["clocks"]
 
     import flash_attention_factory_b200 as pkg
 

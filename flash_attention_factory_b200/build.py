@@ -119,10 +119,14 @@ def main() -> None:
     ap.add_argument("--verbose", action="store_true", help="print ptxas register / smem usage")
     ap.add_argument("--timeline", action="store_true",
                     help="also build libpaged_attention_b200_timeline.so (-DPA_TIMELINE: per-CTA time stamps)")
+    ap.add_argument("--bounds", action="store_true",
+                    help="also build libpaged_attention_b200_bounds.so (-DPA_DEBUG_BOUNDS: range-checked indices)")
     a = ap.parse_args()
     print(build(force=a.force, verbose=a.verbose))
     if a.timeline:
         print(build_variant("timeline", ["-DPA_TIMELINE"]))
+    if a.bounds:
+        print(build_variant("bounds", ["-DPA_DEBUG_BOUNDS"]))
 
 
 if __name__ == "__main__":

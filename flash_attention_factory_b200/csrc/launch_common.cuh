@@ -276,6 +276,7 @@ AttnArgs make_attn_args(const pa_params *p, uint32_t hpc) {
   a.num_kv_heads = p->num_kv_heads;
   a.group = p->num_queries_per_tokens;
   a.max_blocks_per_seq = p->max_blocks_per_seq;
+  a.num_blocks = static_cast<uint32_t>(p->num_blocks); // validated: num_blocks * block_size < 2^31
   a.max_num_partitions = p->max_num_partitions;
   a.block_shift = log2_pow2(p->block_size);
   a.ctx_limit = context_limit(p);
@@ -531,6 +532,22 @@ inline int dispatch_merge(const pa_params *p, cudaStream_t stream) {
   }
 #else
 #define PA_TIMELINE_ACCESSOR(name)
+#endif
+
+// A -DPA_DEBUG_BOUNDS build exports, per launcher, a reader of its unit's range-check report
+// (8 values; see g_bounds_report) that also clears it.  Synchronises the device.
+#ifdef PA_DEBUG_BOUNDS
+#define PA_BOUNDS_ACCESSOR(name)                                                                      \
+  extern "C" PA_API int name(uint32_t *dst) {                                                         \
+    if (dst == nullptr) return ::pa::fail(PA_ERR_BAD_ARG, "bounds report: bad arguments");            \
+    const unsigned int zeros[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};                                   \
+    PA_CUDA_TRY(cudaDeviceSynchronize());                                                             \
+    PA_CUDA_TRY(cudaMemcpyFromSymbol(dst, ::pa::g_bounds_report, sizeof(zeros)));                     \
+    PA_CUDA_TRY(cudaMemcpyToSymbol(::pa::g_bounds_report, zeros, sizeof(zeros)));                     \
+    return PA_OK;                                                                                     \
+  }
+#else
+#define PA_BOUNDS_ACCESSOR(name)
 #endif
 
 // reads and clears this translation unit's copy of the device status word

@@ -11,6 +11,7 @@ int read_status_fp8_loop(int *v) { return read_and_clear_device_status(v); }
 } // namespace pa
 
 PA_TIMELINE_ACCESSOR(pa_debug_timeline_fp8_loop)
+PA_BOUNDS_ACCESSOR(pa_debug_bounds_fp8_loop)
 
 extern "C" PA_API int launch_kernels_fp8_loop(const pa_params *p, void *stream, float *us_out) {
   using namespace pa;

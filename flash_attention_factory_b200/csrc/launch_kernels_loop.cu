@@ -8,6 +8,7 @@ int read_status_loop(int *v) { return read_and_clear_device_status(v); }
 } // namespace pa
 
 PA_TIMELINE_ACCESSOR(pa_debug_timeline_loop)
+PA_BOUNDS_ACCESSOR(pa_debug_bounds_loop)
 
 extern "C" PA_API int launch_kernels_loop(const pa_params *p, void *stream, float *us_out) {
   using namespace pa;

@@ -11,6 +11,7 @@ int read_status_reduce(int *v) { return read_and_clear_device_status(v); }
 } // namespace pa
 
 PA_TIMELINE_ACCESSOR(pa_debug_timeline_reduce)
+PA_BOUNDS_ACCESSOR(pa_debug_bounds_reduce)
 
 extern "C" PA_API int launch_kernels_reduce(const pa_params *p, void *stream, float *us_out) {
   using namespace pa;

@@ -98,6 +98,33 @@ static __device__ unsigned long long g_timeline[kTimelineCtas][8];
 #define PA_STAMP_VALUE(slot, v) do { } while (0)
 #endif
 
+// Range-checked build (-DPA_DEBUG_BOUNDS): every index that the block tables and context
+// lengths can move is checked where it is formed, and the first value found out of range is
+// recorded here instead of being cut or zero-filled silently: [0] findings so far, then the
+// first one as [1] kind, [2] index, [3] limit, [4] sequence, [5] token.  The access itself is
+// made safe either way (index 0 / cut length), so a finding never faults.  One table per
+// translation unit, read and cleared by that unit's pa_debug_bounds_* export.
+enum BoundsKind : unsigned int {
+  BOUNDS_TABLE_INDEX = 1,   // block-table column beyond the sequence's row
+  BOUNDS_BLOCK_ID = 2,      // block id >= num_blocks
+  BOUNDS_CONTEXT_LENGTH = 3 // context length beyond what the row addresses
+};
+#ifdef PA_DEBUG_BOUNDS
+static __device__ unsigned int g_bounds_report[8];
+__device__ __forceinline__ bool bounds_ok(unsigned int kind, uint64_t index, uint64_t limit, uint32_t seq,
+                                          uint32_t tok) {
+  if (index < limit) return true;
+  if (atomicAdd(&g_bounds_report[0], 1u) == 0u) {
+    g_bounds_report[1] = kind;
+    g_bounds_report[2] = static_cast<unsigned int>(min(index, static_cast<uint64_t>(0xffffffffu)));
+    g_bounds_report[3] = static_cast<unsigned int>(min(limit, static_cast<uint64_t>(0xffffffffu)));
+    g_bounds_report[4] = seq;
+    g_bounds_report[5] = tok;
+  }
+  return false;
+}
+#endif
+
 struct AttnArgs {
   const __half *query;
   __half *out;
@@ -112,6 +139,7 @@ struct AttnArgs {
   uint32_t num_kv_heads;
   uint32_t group;
   uint32_t max_blocks_per_seq;
+  uint32_t num_blocks;       // blocks in the cache: the bound of every block id
   uint32_t max_num_partitions;
   uint32_t block_shift;      // log2(block_size)
   uint32_t hpc;              // KV heads per CTA: 1, 2, 4, or 8 in the wide CTA (divides num_kv_heads)
@@ -221,10 +249,16 @@ __device__ __forceinline__ uint32_t load_context(const AttnArgs &args, uint32_t 
   const uint32_t ctx = __ldg(args.context_lens + seq);
   if (args.table_offsets == nullptr) {
     table_off = 0u;
+#ifdef PA_DEBUG_BOUNDS
+    bounds_ok(BOUNDS_CONTEXT_LENGTH, ctx, static_cast<uint64_t>(args.ctx_limit) + 1u, seq, ctx);
+#endif
     return min(ctx, args.ctx_limit);
   }
   table_off = __ldg(args.table_offsets + seq);
   const uint64_t row_tokens = static_cast<uint64_t>(__ldg(args.table_offsets + seq + 1) - table_off) << args.block_shift;
+#ifdef PA_DEBUG_BOUNDS
+  bounds_ok(BOUNDS_CONTEXT_LENGTH, ctx, row_tokens + 1u, seq, ctx);
+#endif
   return static_cast<uint32_t>(min(static_cast<uint64_t>(ctx), row_tokens));
 }
 
@@ -597,7 +631,16 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       if (!it.valid || tok >= it.tok_end) return 0u;
       const size_t row = (args.table_offsets != nullptr) ? static_cast<size_t>(it.table_off)
                                                          : static_cast<size_t>(it.seq) * args.max_blocks_per_seq;
+#ifdef PA_DEBUG_BOUNDS
+      const uint32_t width = (args.table_offsets != nullptr)
+                                 ? __ldg(args.table_offsets + it.seq + 1) - it.table_off
+                                 : args.max_blocks_per_seq;
+      if (!bounds_ok(BOUNDS_TABLE_INDEX, tok >> args.block_shift, width, it.seq, tok)) return 0u;
+      const uint32_t id = __ldg(args.block_tables + row + (tok >> args.block_shift));
+      return bounds_ok(BOUNDS_BLOCK_ID, id, args.num_blocks, it.seq, tok) ? id : 0u;
+#else
       return __ldg(args.block_tables + row + (tok >> args.block_shift));
+#endif
     };
 
     WorkItem cur = first;
@@ -654,7 +697,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         // before it is armed; in steady state the wait for a free stage hides the latency
         float2 lane_scales = make_float2(1.f, 1.f);
         if (block_scales && valid) {
-          const size_t si = static_cast<size_t>(block_id) * args.num_kv_heads + cur.head_base + lane_head;
+          // a block id beyond the cache reads zeros through the descriptor; its scales come from the last block
+          const size_t si = static_cast<size_t>(min(block_id, args.num_blocks - 1u)) * args.num_kv_heads +
+                            cur.head_base + lane_head;
           lane_scales = make_float2(__ldg(args.k_scale_per_block + si), __ldg(args.v_scale_per_block + si));
         }
         for (uint32_t sb = 0; sb < stages_in_batch; ++sb) {
