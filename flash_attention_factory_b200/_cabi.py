@@ -120,6 +120,10 @@ class PaCacheWriteParams(ctypes.Structure):
         ("num_blocks", ctypes.c_uint64),
         ("fp8_scale", ctypes.c_float),
         ("kv_dtype", ctypes.c_int32),
+        ("k_scale_per_head", ctypes.c_void_p),
+        ("v_scale_per_head", ctypes.c_void_p),
+        ("k_scale_per_block", ctypes.c_void_p),
+        ("v_scale_per_block", ctypes.c_void_p),
     ]
 
 

@@ -25,12 +25,16 @@ def _kv_dtype(cache: torch.Tensor) -> int:
 
 
 def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor,
-                      value_cache: torch.Tensor, slot_mapping: torch.Tensor, fp8_scale: float = 1.0) -> None:
+                      value_cache: torch.Tensor, slot_mapping: torch.Tensor, fp8_scale: float = 1.0, *,
+                      k_scale_per_head=None, v_scale_per_head=None,
+                      k_scale_per_block=None, v_scale_per_block=None) -> None:
     """key/value fp16 [T, HK, D] -> caches at slot_mapping[t] = block_id * block_size + row.
 
-    Negative slots are skipped.  FP8 caches store round-to-nearest-even(x / fp8_scale),
-    saturating; the attention operators take the same fp8_scale.  Asynchronous on torch's
-    current stream.
+    Negative slots are skipped.  FP8 caches store round-to-nearest-even(x / scale),
+    saturating, where scale is `fp8_scale` or, when given, the entry of the token's KV head
+    in `k_scale_per_head` / `v_scale_per_head` (float32 [HK]) or of its block and KV head in
+    `k_scale_per_block` / `v_scale_per_block` (float32 [num_blocks, HK]); the attention
+    operators take the same scale arguments.  Asynchronous on torch's current stream.
     """
     if not key.is_cuda:
         raise RuntimeError("reshape_and_cache needs CUDA tensors (no CPU fallback exists)")
@@ -53,6 +57,17 @@ def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.T
     p.block_size, p.num_blocks = key_cache.size(1), key_cache.size(0)
     p.fp8_scale = float(fp8_scale)
     p.kv_dtype = _kv_dtype(key_cache)
+    per_head, per_block = (key.size(1),), (key_cache.size(0), key.size(1))
+    for name, t, shape in (("k_scale_per_head", k_scale_per_head, per_head),
+                           ("v_scale_per_head", v_scale_per_head, per_head),
+                           ("k_scale_per_block", k_scale_per_block, per_block),
+                           ("v_scale_per_block", v_scale_per_block, per_block)):
+        if t is None:
+            continue
+        if (t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous()
+                or t.device != key.device):
+            raise RuntimeError(f"{name} must be a contiguous float32 tensor of shape {shape} on the cache's device")
+        setattr(p, name, t.data_ptr())
     lib = _cabi.load_library()
     with torch.cuda.device(key.device):
         stream = torch.cuda.current_stream(key.device).cuda_stream

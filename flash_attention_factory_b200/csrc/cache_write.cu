@@ -4,8 +4,10 @@
 // kernel: its tests build caches on the host with torch casts (test_paged_fp8cache.py:180-203)
 // in the layout the attention kernels read, [num_blocks, block_size, num_kv_heads, head_size]
 // (paged_attention_kernel_loop.hpp:50-51).  This kernel defines the same contract on the
-// device: value stored = round-to-nearest-even(x / fp8_scale) in e5m2 or e4m3 (saturating to
-// the largest finite code), or x itself for an fp16 cache.
+// device: value stored = round-to-nearest-even(x / scale) in e5m2 or e4m3 (saturating to
+// the largest finite code), or x itself for an fp16 cache.  The scale is fp8_scale, or the
+// entry of the token's KV head (and block) in the per-head / per-block scale arrays that the
+// attention entry points read back under the same names.
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
@@ -47,13 +49,24 @@ __device__ __forceinline__ void store_converted(void *dst_row, uint32_t elem, ui
   }
 }
 
+// Where the scale of an element comes from.
+enum ScaleKind : int { SCALE_SCALAR = 0, SCALE_PER_HEAD = 1, SCALE_PER_BLOCK = 2 };
+
+struct ScaleArrays {
+  const float *k; // [num_kv_heads] or [num_blocks, num_kv_heads]; unused for SCALE_SCALAR
+  const float *v;
+  uint32_t head_size;
+  uint32_t num_kv_heads;
+  uint32_t block_size;
+};
+
 // One CTA per new token; a thread moves 8 elements of K and 8 of V per step.
-template <int KV, bool CHAINED>
+template <int KV, bool CHAINED, int SCALES>
 __global__ void __launch_bounds__(128)
 reshape_and_cache_kernel(const __half *__restrict__ key, const __half *__restrict__ value,
                          void *__restrict__ key_cache, void *__restrict__ value_cache,
                          const int64_t *__restrict__ slot_mapping, uint32_t row_elems, uint64_t num_slots,
-                         float scale, float exact_rcp) {
+                         float scale, float exact_rcp, ScaleArrays arrays) {
   // CHAINED (decode-sized appends): programmatic dependent launch.  The attention kernel that
   // follows in a decode step may be scheduled while this grid runs (it waits for this grid's
   // completion before its first read), and this grid reads nothing before its own predecessor
@@ -75,8 +88,18 @@ reshape_and_cache_kernel(const __half *__restrict__ key, const __half *__restric
   for (uint32_t e = threadIdx.x * 8; e < row_elems; e += blockDim.x * 8) {
     const uint4 kv = __ldg(reinterpret_cast<const uint4 *>(ksrc + e));
     const uint4 vv = __ldg(reinterpret_cast<const uint4 *>(vsrc + e));
-    store_converted<KV>(kdst, e, kv, scale, exact_rcp);
-    store_converted<KV>(vdst, e, vv, scale, exact_rcp);
+    if constexpr (SCALES == SCALE_SCALAR || KV == KV_F16) {
+      store_converted<KV>(kdst, e, kv, scale, exact_rcp);
+      store_converted<KV>(vdst, e, vv, scale, exact_rcp);
+    } else {
+      // 8 elements never straddle a head (head_size is a multiple of 8); always the IEEE division
+      const uint32_t head = e / arrays.head_size;
+      const size_t si = (SCALES == SCALE_PER_HEAD)
+                            ? head
+                            : static_cast<size_t>(slot / arrays.block_size) * arrays.num_kv_heads + head;
+      store_converted<KV>(kdst, e, kv, __ldg(arrays.k + si), 0.f);
+      store_converted<KV>(vdst, e, vv, __ldg(arrays.v + si), 0.f);
+    }
   }
 }
 
@@ -94,7 +117,18 @@ extern "C" PA_API int pa_reshape_and_cache(const pa_cache_write_params *p, void 
   if (row_elems == 0 || row_elems % 8 != 0 || row_elems > (1u << 20))
     return fail(PA_ERR_BAD_ARG, "num_kv_heads * head_size must be a positive multiple of 8");
   if (p->block_size == 0 || p->num_blocks == 0) return fail(PA_ERR_BAD_ARG, "empty cache");
-  if (p->kv_dtype != PA_KV_F16 && !(p->fp8_scale > 0.f))
+  const bool per_head = p->k_scale_per_head != nullptr || p->v_scale_per_head != nullptr;
+  const bool per_block = p->k_scale_per_block != nullptr || p->v_scale_per_block != nullptr;
+  if (per_head && (p->k_scale_per_head == nullptr || p->v_scale_per_head == nullptr))
+    return fail(PA_ERR_BAD_ARG, "k_scale_per_head and v_scale_per_head must be given together");
+  if (per_block && (p->k_scale_per_block == nullptr || p->v_scale_per_block == nullptr))
+    return fail(PA_ERR_BAD_ARG, "k_scale_per_block and v_scale_per_block must be given together");
+  if (per_head && per_block) return fail(PA_ERR_BAD_ARG, "per-head and per-block scales exclude each other");
+  if ((per_head || per_block) && p->kv_dtype == PA_KV_F16)
+    return fail(PA_ERR_BAD_ARG, "scale arrays need an FP8 cache");
+  if ((per_head || per_block) && (p->head_size == 0 || p->head_size % 8 != 0))
+    return fail(PA_ERR_BAD_ARG, "scale arrays need a head_size that is a multiple of 8");
+  if (p->kv_dtype != PA_KV_F16 && !per_head && !per_block && !(p->fp8_scale > 0.f))
     return fail(PA_ERR_BAD_ARG, "fp8_scale must be positive and finite");
   if (!aligned16(p->key) || !aligned16(p->value) || !aligned16(p->key_cache) || !aligned16(p->value_cache))
     return fail(PA_ERR_BAD_ARG, "key / value / caches must be 16-byte aligned");
@@ -103,7 +137,8 @@ extern "C" PA_API int pa_reshape_and_cache(const pa_cache_write_params *p, void 
   float exact_rcp = 0.f;
   {
     int exponent = 0;
-    if (p->kv_dtype != PA_KV_F16 && std::frexp(p->fp8_scale, &exponent) == 0.5f && exponent > -100 && exponent < 100)
+    if (p->kv_dtype != PA_KV_F16 && !per_head && !per_block && std::frexp(p->fp8_scale, &exponent) == 0.5f &&
+        exponent > -100 && exponent < 100)
       exact_rcp = 1.f / p->fp8_scale;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -122,13 +157,31 @@ extern "C" PA_API int pa_reshape_and_cache(const pa_cache_write_params *p, void 
   cfg.numAttrs = chained ? 1 : 0;
   const float scale = (p->kv_dtype == PA_KV_F16) ? 1.f : p->fp8_scale;
   const float rcp = (p->kv_dtype == PA_KV_F16) ? 1.f : exact_rcp;
-  auto kernel = (p->kv_dtype == PA_KV_F16)
-                    ? (chained ? reshape_and_cache_kernel<KV_F16, true> : reshape_and_cache_kernel<KV_F16, false>)
-                : (p->kv_dtype == PA_KV_FP8_E5M2)
-                    ? (chained ? reshape_and_cache_kernel<KV_E5M2, true> : reshape_and_cache_kernel<KV_E5M2, false>)
-                    : (chained ? reshape_and_cache_kernel<KV_E4M3, true> : reshape_and_cache_kernel<KV_E4M3, false>);
+  ScaleArrays arrays{};
+  arrays.k = per_head ? p->k_scale_per_head : p->k_scale_per_block;
+  arrays.v = per_head ? p->v_scale_per_head : p->v_scale_per_block;
+  arrays.head_size = p->head_size;
+  arrays.num_kv_heads = p->num_kv_heads;
+  arrays.block_size = p->block_size;
+  using kernel_fn = void (*)(const __half *, const __half *, void *, void *, const int64_t *, uint32_t, uint64_t,
+                             float, float, ScaleArrays);
+  // [cache type][chained][scale kind]; an fp16 cache has no scales
+  static const kernel_fn table[3][2][3] = {
+      {{reshape_and_cache_kernel<KV_F16, false, SCALE_SCALAR>, nullptr, nullptr},
+       {reshape_and_cache_kernel<KV_F16, true, SCALE_SCALAR>, nullptr, nullptr}},
+      {{reshape_and_cache_kernel<KV_E5M2, false, SCALE_SCALAR>, reshape_and_cache_kernel<KV_E5M2, false, SCALE_PER_HEAD>,
+        reshape_and_cache_kernel<KV_E5M2, false, SCALE_PER_BLOCK>},
+       {reshape_and_cache_kernel<KV_E5M2, true, SCALE_SCALAR>, reshape_and_cache_kernel<KV_E5M2, true, SCALE_PER_HEAD>,
+        reshape_and_cache_kernel<KV_E5M2, true, SCALE_PER_BLOCK>}},
+      {{reshape_and_cache_kernel<KV_E4M3, false, SCALE_SCALAR>, reshape_and_cache_kernel<KV_E4M3, false, SCALE_PER_HEAD>,
+        reshape_and_cache_kernel<KV_E4M3, false, SCALE_PER_BLOCK>},
+       {reshape_and_cache_kernel<KV_E4M3, true, SCALE_SCALAR>, reshape_and_cache_kernel<KV_E4M3, true, SCALE_PER_HEAD>,
+        reshape_and_cache_kernel<KV_E4M3, true, SCALE_PER_BLOCK>}}};
+  const int type_index = (p->kv_dtype == PA_KV_F16) ? 0 : (p->kv_dtype == PA_KV_FP8_E5M2) ? 1 : 2;
+  const int scale_kind = per_head ? SCALE_PER_HEAD : per_block ? SCALE_PER_BLOCK : SCALE_SCALAR;
+  const kernel_fn kernel = table[type_index][chained ? 1 : 0][scale_kind];
   PA_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, k, v, p->key_cache, p->value_cache, p->slot_mapping, re,
-                                 num_slots, scale, rcp));
+                                 num_slots, scale, rcp, arrays));
   PA_CUDA_TRY(cudaGetLastError());
   return PA_OK;
 }

@@ -361,12 +361,21 @@ typedef struct pa_cache_write_params {
   uint64_t num_blocks;
   float fp8_scale;             /* stored = x / fp8_scale (the scale the attention entry points take) */
   int32_t kv_dtype;            /* pa_kv_dtype of the cache */
+  /* Optional scales of an FP8 cache that take the place of fp8_scale, the very arrays the
+   * attention entry points take under the same names (pa_params): per KV head, fp32
+   * [num_kv_heads], or per block and KV head, fp32 [num_blocks, num_kv_heads].  K and V
+   * both or neither, one kind at most; stored = x / scale of the token's head (and block).
+   * All NULL (a zero-initialised tail) = fp8_scale. */
+  const float *k_scale_per_head;
+  const float *v_scale_per_head;
+  const float *k_scale_per_block;
+  const float *v_scale_per_block;
 } pa_cache_write_params;
 
 /* Appends new K/V tokens to the paged cache in the layout the attention entry points read
  * (reference paged_attention_kernel_loop.hpp:50-51), casting to the cache type: fp16 is
- * copied, FP8 is round-to-nearest-even of x / fp8_scale, saturating to the largest finite
- * code.  The reference has no device kernel for this step: its tests fill caches on the host
+ * copied, FP8 is round-to-nearest-even of x / scale (fp8_scale, or the per-head / per-block
+ * scale arrays when given), saturating to the largest finite code.  The reference has no device kernel for this step: its tests fill caches on the host
  * with torch casts (test_paged_fp8cache.py:180-203), which this call reproduces bit for bit for
  * values inside the format's range.  Asynchronous on `stream`. */
 PA_API int pa_reshape_and_cache(const pa_cache_write_params *p, void *stream);

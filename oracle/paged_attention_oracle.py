@@ -209,7 +209,8 @@ def kv_bytes(context_lens: Sequence[int], num_kv_heads: int, head_size: int, elt
 
 
 def reshape_and_cache_ref(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor,
-                          value_cache: torch.Tensor, slot_mapping: torch.Tensor, fp8_scale: float = 1.0):
+                          value_cache: torch.Tensor, slot_mapping: torch.Tensor, fp8_scale: float = 1.0,
+                          k_scales: Optional[torch.Tensor] = None, v_scales: Optional[torch.Tensor] = None):
     """CPU statement of the cache append: returns new (key_cache, value_cache).
 
     Token t goes to flat slot slot_mapping[t] = block_id * block_size + row of the
@@ -217,19 +218,30 @@ def reshape_and_cache_ref(key: torch.Tensor, value: torch.Tensor, key_cache: tor
     paged_attention_loop/paged_attention_kernel_loop.hpp:50-51); negative slots are skipped.
     The cast is the reference fixture's: `x.to(fp8_dtype)` on the fp16 data
     (test_paged_fp8cache.py:201-203), after dividing by the per-tensor scale in fp32.
+    `k_scales` / `v_scales` (an extension over the reference's single scalar) replace the
+    scalar: shape [kv_heads] = one scale per KV head, [num_blocks, kv_heads] = one per block
+    and KV head, the inverse of what `paged_attention_ref` multiplies by.
     """
     kc, vc = key_cache.clone(), value_cache.clone()
     dt = kc.dtype
     flat_k = kc.view(-1, *kc.shape[2:])
     flat_v = vc.view(-1, *vc.shape[2:])
+    block_size = kc.shape[1]
+
+    def divisor(scales, slot):
+        if scales is None:
+            return fp8_scale
+        per_head = scales if scales.dim() == 1 else scales[slot // block_size]
+        return per_head.float().view(-1, 1)  # [kv_heads, 1] against a [kv_heads, head_size] row
+
     for t, slot in enumerate(slot_mapping.tolist()):
         if slot < 0 or slot >= flat_k.shape[0]:
             continue
         if dt == torch.float16:
             flat_k[slot], flat_v[slot] = key[t], value[t]
         else:
-            flat_k[slot] = (key[t].float() / fp8_scale).to(dt)
-            flat_v[slot] = (value[t].float() / fp8_scale).to(dt)
+            flat_k[slot] = (key[t].float() / divisor(k_scales, slot)).to(dt)
+            flat_v[slot] = (value[t].float() / divisor(v_scales, slot)).to(dt)
     return kc, vc
 
 

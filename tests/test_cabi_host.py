@@ -208,6 +208,16 @@ def test_cache_write_validates_on_the_host(lib):
     assert call(fp8_scale=0.0)[0] == _cabi.PA_ERR_BAD_ARG
     assert call(key_cache=0x3004)[0] == _cabi.PA_ERR_BAD_ARG
     assert lib.pa_reshape_and_cache(None, None) == _cabi.PA_ERR_BAD_ARG
+    # scale arrays: K and V together, one kind at most, FP8 caches only
+    rc, msg = call(k_scale_per_head=0x6000)
+    assert rc == _cabi.PA_ERR_BAD_ARG and "together" in msg
+    rc, msg = call(v_scale_per_block=0x6000)
+    assert rc == _cabi.PA_ERR_BAD_ARG and "together" in msg
+    rc, msg = call(k_scale_per_head=0x6000, v_scale_per_head=0x7000, k_scale_per_block=0x8000,
+                   v_scale_per_block=0x9000)
+    assert rc == _cabi.PA_ERR_BAD_ARG and "exclude" in msg
+    rc, msg = call(k_scale_per_block=0x8000, v_scale_per_block=0x9000, kv_dtype=_cabi.KV_F16)
+    assert rc == _cabi.PA_ERR_BAD_ARG and "FP8" in msg
 
 
 def test_static_scratch_refusals_need_no_gpu(lib):

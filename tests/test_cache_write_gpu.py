@@ -95,3 +95,74 @@ def test_prefill_sized_append_is_bit_exact(cuda_device, kv, scale):
     torch.cuda.synchronize(cuda_device)
     assert torch.equal(_bits(dk.cpu()), _bits(want_k))
     assert torch.equal(_bits(dv.cpu()), _bits(want_v))
+
+
+@pytest.mark.parametrize("kv", ["float8_e5m2", "float8_e4m3fn"])
+@pytest.mark.parametrize("kind", ["per_head", "per_block"])
+@pytest.mark.parametrize("hk,d,bs,t", [(8, 128, 16, 37), (2, 64, 64, 21), (4, 128, 16, 5000)])
+def test_append_with_scale_arrays_is_bit_exact(cuda_device, kv, kind, hk, d, bs, t):
+    """Per-head and per-block scale arrays take the place of the scalar: stored = x / scale of
+    the token's KV head (and block), in the arithmetic of the oracle's torch division."""
+    from flash_attention_factory_b200.cache_ops import reshape_and_cache
+
+    g = torch.Generator().manual_seed(hk * 31 + d + bs + t)
+    nb = (t + bs - 1) // bs + 11
+    dt = FP8_DTYPES[kv]
+    shape = (hk,) if kind == "per_head" else (nb, hk)
+    k_scales = torch.rand(shape, generator=g) * 1.5 + 0.05
+    v_scales = torch.rand(shape, generator=g) * 3.0 + 0.01
+    key = (torch.randn(t, hk, d, generator=g) * 2).to(torch.float16)
+    value = (torch.randn(t, hk, d, generator=g) * 2).to(torch.float16)
+    kc = torch.randn(nb, bs, hk, d, generator=g).to(torch.float16).to(dt)
+    vc = torch.randn(nb, bs, hk, d, generator=g).to(torch.float16).to(dt)
+    slots = torch.randperm(nb * bs, generator=g)[:t].to(torch.int64)
+    slots[3] = -1
+    want_k, want_v = oracle.reshape_and_cache_ref(key, value, kc, vc, slots, 123.0, k_scales, v_scales)
+    dk, dv = kc.to(cuda_device), vc.to(cuda_device)
+    names = {f"k_scale_{kind}": k_scales.to(cuda_device), f"v_scale_{kind}": v_scales.to(cuda_device)}
+    # the scalar must be ignored when arrays are given
+    reshape_and_cache(key.to(cuda_device), value.to(cuda_device), dk, dv, slots.to(cuda_device), 123.0, **names)
+    torch.cuda.synchronize(cuda_device)
+    assert torch.equal(_bits(dk.cpu()), _bits(want_k))
+    assert torch.equal(_bits(dv.cpu()), _bits(want_v))
+
+
+@pytest.mark.parametrize("kv", ["float8_e5m2", "float8_e4m3fn"])
+def test_decode_step_with_per_block_scales_append_then_attend(cuda_device, kv):
+    """Writer and reader agree on per-block scales: the kernel appends one token per sequence with
+    the scale of its block, attention with the same arrays equals the oracle on the oracle's cache."""
+    from flash_attention_factory_b200 import lib
+    from flash_attention_factory_b200.cache_ops import reshape_and_cache
+
+    ctx = [100, 511, 512, 37]
+    hk, h, d, bs = 2, 8, 128, 16
+    c = make_case(seed=78, num_seqs=4, num_heads=h, num_kv_heads=hk, head_size=d, block_size=bs,
+                  context_lens=[n + 1 for n in ctx], kv_dtype=kv)
+    g = torch.Generator().manual_seed(5)
+    nb = c["key_cache"].size(0)
+    k_scales = torch.rand(nb, hk, generator=g) * 1.5 + 0.25
+    v_scales = torch.rand(nb, hk, generator=g) * 3.0 + 0.1
+    new_k = torch.randn(4, hk, d, generator=g).to(torch.float16)
+    new_v = torch.randn(4, hk, d, generator=g).to(torch.float16)
+    slots = torch.tensor([int(c["block_tables"][i, n // bs]) * bs + n % bs for i, n in enumerate(ctx)])
+    want_k, want_v = oracle.reshape_and_cache_ref(new_k, new_v, c["key_cache"], c["value_cache"], slots, 1.0,
+                                                  k_scales, v_scales)
+    dev = cuda_device
+    dk, dv = c["key_cache"].to(dev), c["value_cache"].to(dev)
+    ks, vs = k_scales.to(dev), v_scales.to(dev)
+    reshape_and_cache(new_k.to(dev), new_v.to(dev), dk, dv, slots.to(dev), 1.0,
+                      k_scale_per_block=ks, v_scale_per_block=vs)
+    assert torch.equal(_bits(dk.cpu()), _bits(want_k)) and torch.equal(_bits(dv.cpu()), _bits(want_v))
+    want = oracle.paged_attention_ref(c["query"], want_k, want_v, c["block_tables"], c["context_lens"],
+                                      sm_scale=c["sm_scale"], k_block_scales=k_scales, v_block_scales=v_scales)
+    npart = (max(ctx) + 1 + 511) // 512
+    for variant in ("loop", "reduce"):
+        ml = torch.empty(4, h, npart, dtype=torch.float32, device=dev)
+        es, tmp = torch.empty_like(ml), torch.empty(4, h, npart, d, dtype=torch.float16, device=dev)
+        out = torch.zeros(4, h, d, dtype=torch.float16, device=dev)
+        getattr(lib, f"paged_attention_fp8_{variant}").enqueue(
+            ml, es, tmp, out, torch.zeros(1, device=dev), c["query"].to(dev), dk, dv, c["block_tables"].to(dev),
+            c["context_lens"].to(dev), h // hk, c["sm_scale"], 1.0, bs, max(ctx) + 1, torch.ones(h, device=dev),
+            None, -1.0, k_scale_per_block=ks, v_scale_per_block=vs)
+        torch.cuda.synchronize(dev)
+        assert_close(out.cpu(), want, atol=3e-3, rtol=1e-2, what=f"append+attend per-block scales/{kv}/{variant}")
