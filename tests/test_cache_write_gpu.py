@@ -109,8 +109,9 @@ def test_append_with_scale_arrays_is_bit_exact(cuda_device, kv, kind, hk, d, bs,
     nb = (t + bs - 1) // bs + 11
     dt = FP8_DTYPES[kv]
     shape = (hk,) if kind == "per_head" else (nb, hk)
+    # |x / scale| stays inside e4m3's range (448): torch's cast turns overflow into NaN, the kernel saturates
     k_scales = torch.rand(shape, generator=g) * 1.5 + 0.05
-    v_scales = torch.rand(shape, generator=g) * 3.0 + 0.01
+    v_scales = torch.rand(shape, generator=g) * 3.0 + 0.1
     key = (torch.randn(t, hk, d, generator=g) * 2).to(torch.float16)
     value = (torch.randn(t, hk, d, generator=g) * 2).to(torch.float16)
     kc = torch.randn(nb, bs, hk, d, generator=g).to(torch.float16).to(dt)
