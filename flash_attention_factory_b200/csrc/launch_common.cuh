@@ -280,6 +280,8 @@ AttnArgs make_attn_args(const pa_params *p, uint32_t hpc) {
   a.max_num_partitions = p->max_num_partitions;
   a.block_shift = log2_pow2(p->block_size);
   a.ctx_limit = context_limit(p);
+  a.partition_shift = log2_pow2(policy::partition_size);
+  a.whole_context_items = 0u;
   a.table_offsets = p->block_table_offsets;
   a.hpc = hpc;
   a.tokens_per_stage = policy::tokens_per_stage / a.hpc;
@@ -306,8 +308,12 @@ AttnArgs make_attn_args(const pa_params *p, uint32_t hpc) {
 }
 
 // Enqueues the attention kernel of one (D, KV, MODE, CTA shape, stage size) instantiation.
+// `whole_context_items` (split mode only): the persistent kernel on behalf of the loop variant,
+// one work item per (sequence, head group), results straight into `out`, no scratch, no merge.
+// (internal linkage, like everything below that launches the unit's own kernel copies or touches its tables:
+// two launchers may hold the same instantiation, and merged definitions would launch the other unit's kernels)
 template <int D, int KV, int MODE, int NWARPS = 4, int TILES = 1>
-int enqueue_attention(const pa_params *p, cudaStream_t stream, uint32_t hpc) {
+static int enqueue_attention(const pa_params *p, cudaStream_t stream, uint32_t hpc, bool whole_context_items = false) {
   static_assert(NWARPS == 4 || MODE == MODE_SPLIT, "the wide CTA exists for the split variant only");
   static_assert(NWARPS == 4 || TILES == 1, "the wide CTA is built with one tile per stage");
   using L = SmemLayout<D, KV, NWARPS, TILES>;
@@ -317,6 +323,13 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream, uint32_t hpc) {
   if (dev.cc_major < 10) return fail(PA_ERR_CUDA, "this library needs an sm_100a device");
 
   AttnArgs args = make_attn_args<D, KV, NWARPS, TILES>(p, hpc);
+  if (MODE == MODE_SPLIT && whole_context_items) {
+    args.whole_context_items = 1u;
+    args.max_num_partitions = 1u;
+    args.max_logits = nullptr;
+    args.exp_sums = nullptr;
+    args.tmp_out = nullptr;
+  }
   if (MODE == MODE_SPLIT) {
     // one allocator per translation unit, like the counter table it indexes
     // (the legacy default stream cannot be captured, and asking about it while another stream
@@ -346,7 +359,7 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream, uint32_t hpc) {
   if (MODE == MODE_SPLIT) {
     // persistent CTAs, as many as fit on the device, each walking the (seq, partition, kv head) items with
     // stride gridDim.x; the TMA ring keeps streaming across item boundaries
-    const uint64_t items = static_cast<uint64_t>(p->num_kv_heads / args.hpc) * p->max_num_partitions * p->num_seqs;
+    const uint64_t items = static_cast<uint64_t>(p->num_kv_heads / args.hpc) * args.max_num_partitions * p->num_seqs;
     const uint64_t resident = static_cast<uint64_t>(policy::ctas_per_sm) * static_cast<uint64_t>(dev.sm_count);
     cfg.gridDim = dim3(static_cast<unsigned>(items < resident ? items : resident), 1, 1);
     // programmatic dependent launch: back-to-back calls overlap this grid's start-up with the
@@ -377,7 +390,7 @@ int enqueue_attention(const pa_params *p, cudaStream_t stream, uint32_t hpc) {
 }
 
 template <int D>
-int enqueue_merge(const pa_params *p, cudaStream_t stream) {
+static int enqueue_merge(const pa_params *p, cudaStream_t stream) {
   const uint32_t psize = (D == 64) ? 256u : 512u;
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[1];
@@ -486,11 +499,52 @@ bool wants_wide_cta(const pa_params *p) {
   return items >= 2ull * static_cast<uint64_t>(dev.sm_count);
 }
 
+// Loop variant on a batch of many short sequences.  One cluster per (sequence, head group) then
+// means thousands of CTAs that stream a few hundred KB each, and every one of them pays the
+// start-up of a CTA (descriptor, barriers, first table entries, first copies) in the open.  The
+// persistent kernel of the split variant runs the same items from its queue instead, a whole
+// context per item, with the ring streaming across item boundaries; a CTA that holds a whole
+// context holds the final result, so it writes `out` itself and there is still one launch and
+// no scratch.  Taken when there are at least four units per SM and the longest possible item
+// (the context-length hint times the bytes of a token of the CTA's heads) is at most 2 MiB, which
+// bounds what one CTA can still be streaming after the queue has run dry (about 85 us).
+// Measured on B200, 8 KV heads, group 4: 4096 sequences of 64..512 tokens 431 us instead of
+// 1251 us (e5m2) and 756 instead of 1432 us (fp16); 1024 sequences of 512..2048 tokens (e5m2)
+// 446 instead of 545 us (the wide CTA brings nothing here).  Longer or fewer items stay with the clusters: 128 sequences of
+// 1024..8192 tokens 286 us instead of 203 us, 1024 log-normal lengths up to 32768 tokens 1777
+// instead of 1036 us.
+inline bool wants_persistent_loop(const pa_params *p, uint32_t hpc, uint32_t bytes_per_element, int sm_count) {
+  // debugging knob: PA_PERSISTENT_LOOP=0 never, 1 whenever the context-length hint is given
+  static const int knob = [] {
+    const char *e = std::getenv("PA_PERSISTENT_LOOP");
+    return e ? std::atoi(e) : -1;
+  }();
+  const uint32_t hint = context_hint(p);
+  if (knob == 0 || hint == 0u) return false;
+  if (knob == 1) return true;
+  const uint64_t units = static_cast<uint64_t>(p->num_seqs) * (p->num_kv_heads / hpc);
+  const uint64_t longest_item = static_cast<uint64_t>(hint) * hpc * p->head_size * 2ull * bytes_per_element;
+  return units >= 4ull * static_cast<uint64_t>(sm_count) && longest_item <= (2ull << 20);
+}
+
 // stage-size dispatch for one head size, KV type and mode (default CTA shape)
 template <int D, int KV, int MODE>
-int dispatch_stage_tiles(const pa_params *p, cudaStream_t stream) {
+static int dispatch_stage_tiles(const pa_params *p, cudaStream_t stream) {
   DeviceInfo dev{};
   if (int rc = get_device_info(&dev)) return rc;
+  if constexpr (MODE == MODE_LOOP) {
+    const uint32_t hpc_items = choose_heads_per_cta(p, /*wide=*/false, /*loop_mode=*/false, dev.sm_count);
+    if (wants_persistent_loop(p, hpc_items, KV == KV_F16 ? 2u : 1u, dev.sm_count)) {
+      const uint32_t tiles = choose_stage_tiles<D, KV>(p, hpc_items, 4u);
+      if constexpr (max_stage_tiles<D, KV>() >= 4u) {
+        if (tiles == 4u) return enqueue_attention<D, KV, MODE_SPLIT, 4, 4>(p, stream, hpc_items, true);
+      }
+      if constexpr (max_stage_tiles<D, KV>() >= 2u) {
+        if (tiles >= 2u) return enqueue_attention<D, KV, MODE_SPLIT, 4, 2>(p, stream, hpc_items, true);
+      }
+      return enqueue_attention<D, KV, MODE_SPLIT, 4, 1>(p, stream, hpc_items, true);
+    }
+  }
   const uint32_t hpc = choose_heads_per_cta(p, /*wide=*/false, MODE == MODE_LOOP, dev.sm_count);
   const uint32_t tiles = choose_stage_tiles<D, KV>(p, hpc, 4u);
   if constexpr (max_stage_tiles<D, KV>() >= 4u) {
@@ -504,7 +558,7 @@ int dispatch_stage_tiles(const pa_params *p, cudaStream_t stream) {
 
 // head-size dispatch for one KV type and mode
 template <int KV, int MODE>
-int dispatch_head_size(const pa_params *p, cudaStream_t stream) {
+static int dispatch_head_size(const pa_params *p, cudaStream_t stream) {
   if constexpr (KV != KV_F16 && MODE == MODE_SPLIT) {
     if (wants_wide_cta<KV, MODE>(p)) {
       if (p->head_size == 128) return enqueue_attention<128, KV, MODE, 8>(p, stream, 8u);
@@ -515,7 +569,7 @@ int dispatch_head_size(const pa_params *p, cudaStream_t stream) {
   return dispatch_stage_tiles<64, KV, MODE>(p, stream);
 }
 
-inline int dispatch_merge(const pa_params *p, cudaStream_t stream) {
+static inline int dispatch_merge(const pa_params *p, cudaStream_t stream) {
   if (p->head_size == 128) return enqueue_merge<128>(p, stream);
   return enqueue_merge<64>(p, stream);
 }
@@ -551,7 +605,7 @@ inline int dispatch_merge(const pa_params *p, cudaStream_t stream) {
 #endif
 
 // reads and clears this translation unit's copy of the device status word
-inline int read_and_clear_device_status(int *value) {
+static inline int read_and_clear_device_status(int *value) {
   int v = 0, zero = 0;
   PA_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_pa_device_status, sizeof(int)));
   if (v != 0) PA_CUDA_TRY(cudaMemcpyToSymbol(g_pa_device_status, &zero, sizeof(int)));

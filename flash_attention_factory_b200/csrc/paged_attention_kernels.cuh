@@ -70,7 +70,7 @@ static __device__ unsigned int g_sched[kSchedSlots][2];
 static std::atomic<uint32_t> g_next_direct_slot{0};
 static std::atomic<uint32_t> g_next_captured_slot{0};
 
-inline uint32_t next_sched_slot(bool capturing) {
+static inline uint32_t next_sched_slot(bool capturing) { // static like the counters it advances: one per unit
   if (capturing)
     return kDirectSchedSlots +
            g_next_captured_slot.fetch_add(1, std::memory_order_relaxed) % (kSchedSlots - kDirectSchedSlots);
@@ -159,6 +159,12 @@ struct AttnArgs {
   const float *v_scale_per_block;
   float sm_scale_log2;       // sm_scale * log2(e)
   uint32_t sched_slot;       // row of g_sched this launch uses (split mode)
+  // split mode: log2 of the partition size in tokens
+  uint32_t partition_shift;
+  // split mode run on behalf of the loop variant (many short sequences): a work item is the whole
+  // context of a (sequence, head group), its normalised result goes straight to `out`, and the
+  // scratch tensors are neither read nor written (they may be null)
+  uint32_t whole_context_items;
   // max_blocks_per_seq * block_size (saturated to 32 bits): a context length beyond it is cut
   // to it, so no block-table read leaves the sequence's row whatever context_lens holds
   uint32_t ctx_limit;
@@ -273,7 +279,6 @@ __device__ __forceinline__ uint32_t load_context(const AttnArgs &args, uint32_t 
 // sequences in registers (one per lane) and moves it forward as its item numbers grow, so the
 // context lengths are read once per warp over the life of the kernel.  Every method is
 // called by all 32 lanes of a warp together.
-template <uint32_t PARTITION>
 struct SplitCursor {
   uint32_t window_seq;     // first sequence of the window (multiple of 32)
   uint32_t items_before;   // items of all sequences before the window
@@ -283,12 +288,20 @@ struct SplitCursor {
   uint32_t lane_incl;      // items of sequences window_seq .. window_seq + lane (inclusive scan)
   uint32_t window_items;   // items of the whole window
 
+  // partitions of a context that have a number; with whole-context items every sequence of the
+  // launch, an empty one included, is exactly one (its output row has to be written)
+  static __device__ __forceinline__ uint32_t parts_of(const AttnArgs &args, uint32_t ctx) {
+    if (args.whole_context_items != 0u) return 1u;
+    const uint32_t psize = 1u << args.partition_shift;
+    return min((ctx + psize - 1u) >> args.partition_shift, args.max_num_partitions);
+  }
+
   __device__ __forceinline__ void load_window(const AttnArgs &args, uint32_t groups, uint32_t lane) {
     const uint32_t pos = window_seq + lane;
     lane_seq = (pos < args.num_seqs) ? (args.seq_indices != nullptr ? __ldg(args.seq_indices + pos) : pos) : 0u;
     lane_off = 0u;
     lane_ctx = (pos < args.num_seqs) ? load_context(args, lane_seq, lane_off) : 0u;
-    const uint32_t parts = min(divide_round_up(lane_ctx, PARTITION), args.max_num_partitions);
+    const uint32_t parts = (pos < args.num_seqs) ? parts_of(args, lane_ctx) : 0u;
     uint32_t v = parts * groups;
 #pragma unroll
     for (uint32_t o = 1; o < 32; o <<= 1) {
@@ -322,14 +335,19 @@ struct SplitCursor {
     const uint32_t owner = __ffs(__ballot_sync(0xffffffffu, lane_incl > local)) - 1u;
     const uint32_t incl = __shfl_sync(0xffffffffu, lane_incl, owner);
     const uint32_t ctx = __shfl_sync(0xffffffffu, lane_ctx, owner);
-    const uint32_t parts = min(divide_round_up(ctx, PARTITION), args.max_num_partitions);
+    const uint32_t parts = parts_of(args, ctx);
     const uint32_t within = local - (incl - parts * groups); // item number inside the sequence
     it.linear = index;
     it.seq = __shfl_sync(0xffffffffu, lane_seq, owner);
     it.partition = within / groups;
     it.head_base = (within - it.partition * groups) * args.hpc;
-    it.tok_begin = it.partition * PARTITION;
-    it.tok_end = min(ctx, it.tok_begin + PARTITION);
+    if (args.whole_context_items != 0u) {
+      it.tok_begin = 0u;
+      it.tok_end = ctx;
+    } else {
+      it.tok_begin = it.partition << args.partition_shift;
+      it.tok_end = min(ctx, it.tok_begin + (1u << args.partition_shift));
+    }
     it.ctx = ctx;
     it.table_off = __shfl_sync(0xffffffffu, lane_off, owner);
     it.valid = true;
@@ -460,6 +478,12 @@ __device__ __noinline__ void merge_cluster_rows(float *areas, __half *out, const
   }
 }
 
+// Internal linkage: the kernel reads and writes the per-unit tables above (scheduler counters,
+// status word, time stamps, range-check report), and two launchers may build the same
+// instantiation (the loop launchers also run the persistent form).  With external linkage the
+// host stubs of such twins would be merged and a launch could run the other unit's copy, with
+// the other unit's tables behind this unit's slot allocator.
+namespace {
 template <int D, int KV, int MODE, int NWARPS = 4, int TILES = 1>
 __global__ void __launch_bounds__(paged_attention_policy_v2<D, KV, NWARPS, TILES>::threads_per_cta,
                                   paged_attention_policy_v2<D, KV, NWARPS, TILES>::ctas_per_sm)
@@ -531,7 +555,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   // its own cursor over the item numbering and walks it in step with its own loop
   uint32_t cta_rank = 0, num_ranks = 1;
   WorkItem first{};
-  SplitCursor<policy::partition_size> cursor{};
+  SplitCursor cursor{};
   const uint32_t head_groups = args.num_kv_heads / hpc;
   if constexpr (MODE == MODE_SPLIT) {
     // let the merge kernel's CTAs be scheduled as this grid's CTAs retire (it waits for the
@@ -741,6 +765,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
       }
       if (!next_known && alive) resolve_next();
+      // an item without tokens (empty context, whole-context items) ran no batch, so nothing has
+      // fetched the next item's first table entries yet
+      if (total_chunks == 0u) block_id_next = fetch_block_id(nxt, lane_chunk);
       cur = nxt;
       ++item_no;
     }
@@ -1201,6 +1228,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           // ---- one warp per KV head: the warp holds the whole partition, write it out
           // (max_logits / exp_sums / tmp_out, reference paged_attention_kernel_v2.hpp:425-442,532-546)
           const size_t head0 = static_cast<size_t>(cur.seq) * args.num_heads + kv_head * G;
+          const bool whole = args.whole_context_items != 0u;
 #pragma unroll
           for (uint32_t j = 0; j < 2; ++j) {
             const uint32_t g = 2 * t4 + j;
@@ -1208,9 +1236,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
               const size_t pidx = (head0 + g) * args.max_num_partitions + cur.partition;
               // report the true maximum; the sum is re-expressed relative to it
               const float l_true = l_run[j] * fast_exp2(m_ref[j] - m_true[j]);
-              // normalised inside the partition (reference paged_attention_kernel_v2.hpp:386)
+              // normalised inside the partition (reference paged_attention_kernel_v2.hpp:386);
+              // a whole-context item is the final result and goes to its row of `out`
               const float inv = (l_run[j] > 0.f) ? (out_scale / l_run[j]) : 0.f;
-              __half *dst = args.tmp_out + pidx * D;
+              __half *dst = whole ? args.out + (head0 + g) * D : args.tmp_out + pidx * D;
               if constexpr (KV == KV_F16) {
 #pragma unroll
                 for (uint32_t i = 0; i < KSTEPS; ++i) {
@@ -1227,7 +1256,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
                       pack_half2(acc[2 * q][2 + j] * inv, acc[2 * q + 1][2 + j] * inv);
                 }
               }
-              if (gid == 0) {
+              if (gid == 0 && !whole) {
                 args.max_logits[pidx] = m_true[j] * kLn2;
                 args.exp_sums[pidx] = l_true;
               }
@@ -1325,8 +1354,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
               packed.y = pack_half2(lo.z * inv, lo.w * inv);
               packed.z = pack_half2(hi.x * inv, hi.y * inv);
               packed.w = pack_half2(hi.z * inv, hi.w * inv);
-              *reinterpret_cast<uint4 *>(args.tmp_out + pidx * D + d0) = packed;
-              if (d0 == 0) {
+              const bool whole = args.whole_context_items != 0u;
+              __half *dst = whole ? args.out + head * D : args.tmp_out + pidx * D;
+              *reinterpret_cast<uint4 *>(dst + d0) = packed;
+              if (d0 == 0 && !whole) {
                 args.max_logits[pidx] = mt_all * kLn2;
                 args.exp_sums[pidx] = l_all * fast_exp2(mr_all - mt_all);
               }
@@ -1405,6 +1436,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
   // which is the producer lane once the copies in flight have landed (see above)
   if (*abort_flag != 0u && threadIdx.x == 32) atomicExch(&g_pa_device_status, 4);
 }
+} // namespace
 
 // Context length as the attention kernel cut it (load_context): the merge reads exactly the
 // partitions that kernel wrote.
