@@ -67,16 +67,21 @@ def config_spec(name: str) -> dict:
     ref = dict(variant="loop", num_seqs=64, kv_heads=8, ctx=("const", 1500), head_size=64, block_size=64, sinks=True)
     specs["refperf16"] = dict(ref, kv="float16", heads=64)
     specs["refperf8"] = dict(ref, kv="float8_e5m2", heads=40)
+    # many short sequences (no BASELINE counterpart): the batch shape of short-prompt serving, where the
+    # loop variant runs its persistent form (one work item per sequence and head group)
+    specs["short"] = dict(variant="loop", kv="float8_e5m2", num_seqs=4096, heads=32, kv_heads=8,
+                          ctx=("uniform", 64, 512))
     s = dict(head_size=128, block_size=16, sinks=False)
     s.update(specs[name])
     s["name"] = name
     return s
 
 
-CONFIG_SEEDS = {"c1": 1, "c2": 2, "c3": 3, "c4": 4, "c5": 5, "refperf16": 6, "refperf8": 7}
+CONFIG_SEEDS = {"c1": 1, "c2": 2, "c3": 3, "c4": 4, "c5": 5, "refperf16": 6, "refperf8": 7, "short": 8}
 CONFIG_TITLES = {"c1": "BASELINE config 1", "c2": "BASELINE config 2", "c3": "BASELINE config 3",
                  "c4": "BASELINE config 4", "c5": "BASELINE config 5",
-                 "refperf16": "reference perf-mode shape (fp16)", "refperf8": "reference perf-mode shape (fp8)"}
+                 "refperf16": "reference perf-mode shape (fp16)", "refperf8": "reference perf-mode shape (fp8)",
+                 "short": "4096 sequences of 64..512 tokens (no BASELINE counterpart)"}
 
 
 def draw_context_lens(spec: dict, seed: int) -> torch.Tensor:
@@ -693,6 +698,8 @@ VARIANT_TABLE = [
     ("refperf16_launch_kernels_loop", "refperf16", "loop", None),
     ("refperf16_launch_kernels_reduce", "refperf16", "reduce", None),
     ("refperf8_launch_kernels_fp8_loop", "refperf8", "loop", None),
+    ("short_launch_kernels_fp8_loop", "short", "loop", None),
+    ("short_launch_kernels_loop_f16kv", "short", "loop", "float16"),
 ]
 
 
@@ -724,9 +731,10 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="c5",
-                    choices=["c1", "c2", "c3", "c4", "c5", "refperf16", "refperf8", "kvwrite"],
+                    choices=["c1", "c2", "c3", "c4", "c5", "refperf16", "refperf8", "short", "kvwrite"],
                     help="c1..c5: BASELINE configs of the attention path; refperf16 / refperf8: the shapes the "
-                         "reference's perf mode times; kvwrite: the cache-append kernel")
+                         "reference's perf mode times; short: 4096 sequences of 64..512 tokens; kvwrite: the "
+                         "cache-append kernel")
     ap.add_argument("--variant", default=None, choices=["loop", "reduce", "auto"],
                     help="override the entry point the configuration names")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
