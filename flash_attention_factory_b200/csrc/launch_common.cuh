@@ -508,11 +508,11 @@ bool wants_wide_cta(const pa_params *p) {
 // no scratch.  Taken when there are at least four units per SM and the longest possible item
 // (the context-length hint times the bytes of a token of the CTA's heads) is at most 2 MiB, which
 // bounds what one CTA can still be streaming after the queue has run dry (about 85 us).
-// Measured on B200, 8 KV heads, group 4: 4096 sequences of 64..512 tokens 431 us instead of
-// 1251 us (e5m2) and 756 instead of 1432 us (fp16); 1024 sequences of 512..2048 tokens (e5m2)
-// 446 instead of 545 us (the wide CTA brings nothing here).  Longer or fewer items stay with the clusters: 128 sequences of
-// 1024..8192 tokens 286 us instead of 203 us, 1024 log-normal lengths up to 32768 tokens 1777
-// instead of 1036 us.
+// Measured on B200, 8 KV heads, group 4: 4096 sequences of 64..512 tokens 382 us instead of
+// 1251 us (e5m2) and 732 instead of 1432 us (fp16); 1024 sequences of 512..2048 tokens (e5m2)
+// 381 instead of 545 us (the wide CTA brings nothing here).  Longer or fewer items stay with
+// the clusters: 128 sequences of 1024..8192 tokens 286 us instead of 203 us, 1024 log-normal
+// lengths up to 32768 tokens 1777 instead of 1036 us.
 inline bool wants_persistent_loop(const pa_params *p, uint32_t hpc, uint32_t bytes_per_element, int sm_count) {
   // debugging knob: PA_PERSISTENT_LOOP=0 never, 1 whenever the context-length hint is given
   static const int knob = [] {

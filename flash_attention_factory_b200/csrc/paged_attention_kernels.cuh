@@ -315,6 +315,7 @@ struct SplitCursor {
   __device__ __forceinline__ void init(const AttnArgs &args, uint32_t groups, uint32_t lane) {
     window_seq = 0;
     items_before = 0;
+    if (args.whole_context_items != 0u) return; // the numbering needs no running sums there
     load_window(args, groups, lane);
   }
 
@@ -323,6 +324,23 @@ struct SplitCursor {
                                            uint32_t lane) {
     WorkItem it{};
     it.valid = false;
+    if (args.whole_context_items != 0u) {
+      // every sequence has `groups` items: the number gives the sequence directly.  (Walking the
+      // windows instead costs a CTA several dependent loads per draw when the items are small:
+      // between two draws of one CTA all the others have moved the numbering on by several windows.)
+      const uint32_t pos = index / groups;
+      if (pos >= args.num_seqs) return it; // past the last item
+      it.linear = index;
+      it.seq = (args.seq_indices != nullptr) ? __ldg(args.seq_indices + pos) : pos;
+      it.partition = 0u;
+      it.head_base = (index - pos * groups) * args.hpc;
+      it.table_off = 0u;
+      it.ctx = load_context(args, it.seq, it.table_off);
+      it.tok_begin = 0u;
+      it.tok_end = it.ctx;
+      it.valid = true;
+      return it;
+    }
     if (index < items_before) init(args, groups, lane); // never happens with increasing numbers
     while (index >= items_before + window_items) {
       if (window_seq + 32 >= args.num_seqs) return it; // past the last item
@@ -699,19 +717,16 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
       };
       const uint32_t total_chunks = divide_round_up(cur.tok_end - cur.tok_begin, rows);
       const int32_t head_coord = static_cast<int32_t>(cur.head_base + lane_head);
-      // The number is needed at the item's last batch, which prefetches the next item's table
-      // entries; the consumers ask for it when they have consumed this item's last stage.
+      // The number is needed when the item's last batch of copies has been issued: the next
+      // item's context length and first table entries are then fetched while those copies fly
+      // (a short item would otherwise wait for them before its only copies).  The consumers ask
+      // for the number when they have consumed this item's last stage.
       for (uint32_t chunk0 = 0; chunk0 < total_chunks && alive; chunk0 += chunks_per_batch) {
-        if (!next_known && chunk0 + chunks_per_batch >= total_chunks) {
-          resolve_next();
-          if (!alive) break;
-        }
+        const bool last_batch = chunk0 + chunks_per_batch >= total_chunks;
         const uint32_t chunk = chunk0 + lane_chunk;
         const uint32_t block_id = block_id_next;
-        // prefetch the table entries of the next batch (of this item or of the next one)
-        block_id_next = (chunk0 + chunks_per_batch < total_chunks)
-                            ? fetch_block_id(cur, chunk + chunks_per_batch)
-                            : fetch_block_id(nxt, lane_chunk);
+        // prefetch the table entries of this item's next batch
+        if (!last_batch) block_id_next = fetch_block_id(cur, chunk + chunks_per_batch);
         const bool valid = chunk < total_chunks;
         const uint32_t tok = cur.tok_begin + chunk * rows;
         const int32_t y = static_cast<int32_t>((block_id << args.block_shift) + (tok & row_mask));
@@ -764,10 +779,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k,
           }
         }
       }
+      // (also reached by an item without tokens: an empty context as a whole-context item)
       if (!next_known && alive) resolve_next();
-      // an item without tokens (empty context, whole-context items) ran no batch, so nothing has
-      // fetched the next item's first table entries yet
-      if (total_chunks == 0u) block_id_next = fetch_block_id(nxt, lane_chunk);
+      block_id_next = fetch_block_id(nxt, lane_chunk);
       cur = nxt;
       ++item_no;
     }
