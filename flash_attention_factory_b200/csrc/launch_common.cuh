@@ -510,7 +510,7 @@ bool wants_wide_cta(const pa_params *p) {
 // bounds what one CTA can still be streaming after the queue has run dry (about 85 us).
 // Measured on B200, 8 KV heads, group 4: 4096 sequences of 64..512 tokens 382 us instead of
 // 1251 us (e5m2) and 732 instead of 1432 us (fp16); 1024 sequences of 512..2048 tokens (e5m2)
-// 446 instead of 545 us before the item lookup became a division (the wide CTA brings nothing here).  Longer or fewer items stay with
+// 436 instead of 544 us (the wide CTA brings nothing here).  Longer or fewer items stay with
 // the clusters: 128 sequences of 1024..8192 tokens 286 us instead of 203 us, 1024 log-normal
 // lengths up to 32768 tokens 1777 instead of 1036 us.
 inline bool wants_persistent_loop(const pa_params *p, uint32_t hpc, uint32_t bytes_per_element, int sm_count) {
