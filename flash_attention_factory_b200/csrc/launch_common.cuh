@@ -185,7 +185,8 @@ inline uint32_t context_hint(const pa_params *p) { return std::min(p->max_contex
 
 // Cluster size of the loop variant: enough CTAs to give every SM two, using
 // only what the host knows (num_seqs, num_kv_heads and the context-length hint).
-inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_count, uint32_t tokens_per_stage) {
+inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_count, uint32_t tokens_per_stage,
+                                    uint32_t bytes_per_element) {
 #ifdef PA_TUNING_KNOBS
   // tuning build only: PA_LOOP_CLUSTER=1..8 forces the cluster size
   static const int forced = [] {
@@ -206,6 +207,18 @@ inline uint32_t choose_cluster_size(const pa_params *p, uint32_t hpc, int sm_cou
   const uint64_t slots = 2ull * static_cast<uint64_t>(sm_count);
   uint32_t cs = units >= slots ? 1u : static_cast<uint32_t>(std::min<uint64_t>(8ull, slots / units));
   if (cs == 1 && (units < 2 * slots || context_hint(p) == 0 || context_hint(p) >= 2048u)) cs = 2;
+  // With few units one long sequence can outlast all the others together: a CTA streams about
+  // 25-45 GB/s, so a unit of 32 MB on two CTAs takes 500 us whatever else the launch holds.  Up to
+  // two waves of units, the cluster grows until a CTA's share of the longest possible unit is at
+  // most 4 MiB (128 log-normal contexts up to 32768 tokens, 8 KV heads, e5m2: 174 us with 8 CTAs per
+  // unit, 509 us with 2; uniform batches of 8192-token contexts keep their 2, where 4 are 5 %
+  // and 8 are 20 % slower).
+  if (context_hint(p) != 0 && units < 2 * slots) {
+    const uint64_t longest_unit =
+        static_cast<uint64_t>(context_hint(p)) * hpc * p->head_size * 2ull * bytes_per_element;
+    const uint64_t wanted = (longest_unit + (4ull << 20) - 1) / (4ull << 20);
+    cs = static_cast<uint32_t>(std::min<uint64_t>(8ull, std::max<uint64_t>(cs, wanted)));
+  }
   if (context_hint(p) != 0) {
     // a CTA should own at least kMinStagesPerCta stages of the longest context: below that the
     // cluster merge and the extra CTAs cost more than the split saves
@@ -371,7 +384,7 @@ static int enqueue_attention(const pa_params *p, cudaStream_t stream, uint32_t h
   } else {
     // portable cluster sizes only: 9..16 CTAs per cluster measured 30-40 % slower on B200
     // (fewer clusters fit a GPC at once)
-    const uint32_t cs = choose_cluster_size(p, args.hpc, dev.sm_count, args.tokens_per_stage);
+    const uint32_t cs = choose_cluster_size(p, args.hpc, dev.sm_count, args.tokens_per_stage, KV == KV_F16 ? 2u : 1u);
     // the order in which clusters start only matters when they do not all fit at once
     const uint64_t ctas = static_cast<uint64_t>(cs) * (p->num_kv_heads / args.hpc) * p->num_seqs;
     args.longest_first_hint = (ctas > 2ull * static_cast<uint64_t>(dev.sm_count)) ? context_hint(p) : 0u;
