@@ -152,3 +152,22 @@ def test_garbage_past_the_context_is_ignored(cuda_device, kv):
             raw[blk, n % 64:] = nan_bits
     for variant in VARIANTS:
         assert_close(run_entry(variant, c, cuda_device)["out"], want, what=f"garbage/{kv}/{variant}")
+
+
+@pytest.mark.parametrize("kv", ["float16", "float8_e5m2"])
+def test_ragged_batch_with_one_long_sequence(cuda_device, kv):
+    """A few hundred units and a long context-length hint: the loop variant takes clusters of 8, so
+    that the long sequence is spread over 8 CTAs, and most CTAs of the short sequences' clusters get
+    no token.  The block tables draw from a small shared pool (sequences may read the same blocks)."""
+    g = torch.Generator().manual_seed(123)
+    n, long_ctx, pool = 200, 24000, 2048
+    ctx = [long_ctx] + torch.randint(1, 600, (n - 1,), generator=g).tolist()
+    ctx[7], ctx[8], ctx[9] = 0, 1, 16
+    c = make_case(seed=321, num_seqs=1, num_heads=8, num_kv_heads=2, head_size=128, block_size=16,
+                  context_lens=[16 * pool], kv_dtype=kv, sinks=True)  # one sequence's worth of blocks = the pool
+    c["query"] = torch.randn(n, 8, 128, generator=g).to(torch.float16)
+    c["block_tables"] = torch.randint(0, pool, (n, long_ctx // 16), generator=g).to(torch.int32)
+    c["context_lens"] = torch.tensor(ctx, dtype=torch.int32)
+    want = oracle_out(c)
+    for variant in VARIANTS:
+        assert_close(run_entry(variant, c, cuda_device)["out"], want, what=f"ragged/{kv}/{variant}")
