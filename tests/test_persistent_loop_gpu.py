@@ -98,11 +98,12 @@ def test_subset_launch_and_packed_tables(cuda_device):
 
 
 def test_parity_suites_with_the_persistent_loop_forced(cuda_device):
-    """The ordinary parity, bookkeeping and modifier suites once more with every loop launch that
-    carries a context-length hint sent through the persistent kernel."""
+    """The ordinary parity, bookkeeping, modifier, graph-capture, host-step and selector suites once
+    more with every loop launch that carries a context-length hint sent through the persistent kernel."""
     env = dict(os.environ, PA_PERSISTENT_LOOP="1")
     files = ["tests/test_parity_gpu.py", "tests/test_bookkeeping_gpu.py", "tests/test_score_modifiers_gpu.py",
-             "tests/test_per_head_scales_gpu.py", "tests/test_per_block_scales_gpu.py", "tests/test_context_clamp_gpu.py"]
+             "tests/test_per_head_scales_gpu.py", "tests/test_per_block_scales_gpu.py", "tests/test_context_clamp_gpu.py",
+             "tests/test_cuda_graph_gpu.py", "tests/test_host_step_gpu.py", "tests/test_serving_gpu.py"]
     res = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-m", "gpu", "-k", "not persistent", *files],
                          cwd=str(ROOT), env=env, capture_output=True, text=True, timeout=1500)
     assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-2000:]
